@@ -1,0 +1,247 @@
+/*
+ * mk36.h - C ABI of the B200 (sm_100a) Qwen3.6 single-token decode kernels.
+ *
+ * One shared library (libmk36.so) exports these entry points.  They take plain device
+ * pointers, sizes and a CUDA stream handle; there are no PyTorch types in any signature.  The
+ * PyTorch extension `mega_kernel_qwen36._C` is a thin shim over them, and any other host
+ * (ctypes, cgo, JNI, ...) can bind the same symbols.
+ *
+ * Conventions
+ *   - every pointer in an args struct is a DEVICE pointer on the current device unless said
+ *     otherwise; tensors are dense row-major ("contiguous") in the layouts named below;
+ *   - `stream` is a `cudaStream_t` passed as `void*` (NULL = the legacy default stream); calls
+ *     are asynchronous with respect to the host;
+ *   - entry points return MK36_OK (0) or a negative mk36_status; mk36_last_error() then holds a
+ *     human-readable message for the calling thread;
+ *   - the library never allocates or frees device memory.  Kernels that need scratch memory or
+ *     a grid-wide barrier take a caller-owned `workspace` (see mk36_workspace_*).  A workspace
+ *     must not be used by two kernels that may run concurrently (use one per stream);
+ *   - inputs are never written.
+ *
+ * Each entry point names the interface of the reference implementation
+ * (MarcoDotIO/Mega-Kernel-3.6) that it replaces, as file:line within that project.
+ */
+#ifndef MK36_H_
+#define MK36_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define MK36_API __declspec(dllexport)
+#else
+#define MK36_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mk36_dtype {
+    MK36_BF16 = 0,
+    MK36_F16 = 1,
+    MK36_F32 = 2
+} mk36_dtype;
+
+typedef enum mk36_status {
+    MK36_OK = 0,
+    MK36_ERR_INVALID_ARG = -1,   /* null pointer, non-positive size, inconsistent fields */
+    MK36_ERR_UNSUPPORTED = -2,   /* a shape or dtype outside what the kernels handle */
+    MK36_ERR_LAUNCH = -3,        /* the CUDA runtime refused a launch or a query */
+    MK36_ERR_WORKSPACE = -4,     /* workspace missing, misaligned or too small */
+    MK36_ERR_BARRIER_TIMEOUT = -5 /* a bounded device-side wait ran out (see workspace_status) */
+} mk36_status;
+
+/* Library version: major*10000 + minor*100 + patch. */
+MK36_API int mk36_version(void);
+
+/* Message of the last failing call made by this host thread ("" if none). */
+MK36_API const char* mk36_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Workspace.  The reference allocates fresh scratch tensors with torch::empty on every call
+ * (csrc/persistent_moe_decode.cu:732-745, csrc/attention_decode.cu:177-182); here the caller
+ * owns one buffer per (device, stream) instead.
+ *
+ * mk36_workspace_bytes()       size that is enough for every op at the measured shapes
+ *                              (batch <= 8 per launch); 256-byte alignment is required.
+ * mk36_workspace_init()        zeroes the control block (barrier counters, status word).  Must
+ *                              run once before first use and after any reported timeout.
+ * mk36_workspace_status()      synchronises `stream` and returns the device status word in
+ *                              *device_status: 0 = clean, otherwise the code of the bounded wait
+ *                              that gave up (MK36_ERR_BARRIER_TIMEOUT is returned as well).
+ * ------------------------------------------------------------------------------------------ */
+MK36_API size_t mk36_workspace_bytes(void);
+MK36_API int mk36_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_status);
+
+/* Test hook for the give-up path of the bounded device-side waits: launches two CTAs whose barrier
+ * expects a third arrival that never comes; each wait returns after `limit_ms` (1..2000) and
+ * records its code in the status word, so that mk36_workspace_status then reports
+ * MK36_ERR_BARRIER_TIMEOUT.  Nothing hangs or faults; the workspace must be initialised again
+ * afterwards.  No counterpart in the reference (its grid.sync() calls are unbounded:
+ * csrc/persistent_moe_decode.cu:517-564). */
+MK36_API int mk36_selftest_bounded_wait(void* workspace, size_t workspace_bytes, void* stream, int limit_ms);
+
+/* ---------------------------------------------------------------------------------------------
+ * MoE decode: RMSNorm -> router logits -> top-k -> softmax over the k survivors -> routed
+ * SwiGLU experts + shared SwiGLU expert -> down projections -> (+ residual).
+ *
+ * Replaces `moe_decode_persistent_cuda` (csrc/persistent_moe_decode.cu:701-860, bound at
+ * csrc/bindings.cpp:33) and the grouped torch path `_moe_decode_grouped_torch`
+ * (mega_kernel_qwen36/ops.py:161-199); results follow `moe_decode_reference`
+ * (mega_kernel_qwen36/reference.py:16-62), including the rounding of the normalised input to
+ * the activation dtype before the projections.
+ *
+ * Layouts: x [batch, hidden]; norm_weight [hidden]; router_weight [experts, hidden];
+ * expert_gate, expert_up [local_experts, intermediate, hidden];
+ * expert_down [local_experts, hidden, intermediate]; shared_gate, shared_up
+ * [shared_intermediate, hidden]; shared_down [hidden, shared_intermediate];
+ * out [batch, hidden] (same dtype as x); indices [batch, top_k] int64, sorted by descending
+ * logit; route_weights [batch, top_k] fp32.
+ *
+ * Expert parallelism: a rank that holds experts [expert_base, expert_base + local_experts)
+ * passes only those slabs; routing is still computed over all `experts` router rows, and only
+ * the selected experts that are local contribute.  With partial_out != NULL the kernel writes
+ * the fp32 partial sum [batch, hidden] (no residual, no rounding) there instead of `out`
+ * (out may then be NULL); the caller reduces the partials across ranks and adds the residual.
+ * The shared expert is split by passing a slice of its intermediate rows/columns.
+ * Single-GPU callers set expert_base = 0, local_experts = experts, partial_out = NULL.
+ *
+ * experts == 0 && top_k == 0 runs the shared path only (that is a dense SwiGLU FFN).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mk36_moe_args {
+    const void* x;
+    const void* norm_weight;
+    const void* router_weight;
+    const void* expert_gate;
+    const void* expert_up;
+    const void* expert_down;
+    const void* shared_gate;
+    const void* shared_up;
+    const void* shared_down;
+    void* out;
+    int64_t* indices;
+    float* route_weights;
+    float* partial_out;
+    int32_t dtype; /* mk36_dtype of x, every weight and out */
+    int32_t batch;
+    int32_t hidden;
+    int32_t experts;
+    int32_t top_k;
+    int32_t intermediate;
+    int32_t shared_intermediate;
+    int32_t expert_base;
+    int32_t local_experts;
+    int32_t add_residual;
+    float eps;
+} mk36_moe_args;
+
+MK36_API size_t mk36_moe_workspace_bytes(const mk36_moe_args* args);
+MK36_API int mk36_moe_decode(const mk36_moe_args* args, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Dense SwiGLU FFN decode: RMSNorm -> silu(x Wg^T) * (x Wu^T) -> Wd -> (+ residual).
+ *
+ * The reference has no native kernel for this op; this replaces `_dense_ffn_decode_torch`
+ * (mega_kernel_qwen36/ops.py:202-218) and `dense_ffn_decode_triton`
+ * (mega_kernel_qwen36/triton_ops.py:94-109); results follow `dense_ffn_decode_reference`
+ * (mega_kernel_qwen36/reference.py:65-88).
+ *
+ * Layouts: x [batch, hidden]; norm_weight [hidden]; gate_weight, up_weight
+ * [intermediate, hidden]; down_weight [hidden, intermediate]; out [batch, hidden].
+ *
+ * Tensor parallelism: a rank passes its row slice of gate/up and the matching column slice of
+ * down stored densely as [hidden, intermediate_local]; with partial_out != NULL the fp32 partial
+ * [batch, hidden] is written (no residual) for the caller's all-reduce.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mk36_dense_ffn_args {
+    const void* x;
+    const void* norm_weight;
+    const void* gate_weight;
+    const void* up_weight;
+    const void* down_weight;
+    void* out;
+    float* partial_out;
+    int32_t dtype;
+    int32_t batch;
+    int32_t hidden;
+    int32_t intermediate;
+    int32_t add_residual;
+    float eps;
+} mk36_dense_ffn_args;
+
+MK36_API size_t mk36_dense_ffn_workspace_bytes(const mk36_dense_ffn_args* args);
+MK36_API int mk36_dense_ffn_decode(const mk36_dense_ffn_args* args, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Full-attention GQA decode of one query token over an existing KV cache (soft-max over the
+ * whole cache, no causal mask): out[b,h,:] = softmax(scale * q[b,h,:] . K[b,:,h/g,:]) V[b,:,h/g,:].
+ *
+ * Replaces `full_attention_decode_cuda` (csrc/attention_decode.cu:152-218, bound at
+ * csrc/bindings.cpp:34); results follow `full_attention_decode_reference`
+ * (mega_kernel_qwen36/reference.py:117-145).
+ *
+ * Layouts: q, out [batch, query_heads, head_dim]; k_cache, v_cache
+ * [batch, seq_len, kv_heads, head_dim].  query_heads % kv_heads == 0, head_dim <= 256,
+ * seq_len > 0.  KV-head parallel ranks simply pass their own head slices.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mk36_attention_args {
+    const void* q;
+    const void* k_cache;
+    const void* v_cache;
+    void* out;
+    int32_t dtype;
+    int32_t batch;
+    int32_t query_heads;
+    int32_t kv_heads;
+    int32_t head_dim;
+    int32_t seq_len;
+    float scale;
+} mk36_attention_args;
+
+MK36_API size_t mk36_attention_workspace_bytes(const mk36_attention_args* args);
+MK36_API int mk36_full_attention_decode(const mk36_attention_args* args, void* workspace,
+                                        size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Linear-attention recurrent decode step with an fp32 state:
+ *     S'[b,h] = decay * S[b,h] + k[b,hk] (x) (beta * v[b,h]);   out[b,h] = q[b,hk]^T S'[b,h]
+ *
+ * Replaces `linear_attention_decode_cuda` (csrc/linear_attention_decode.cu:46-93, bound at
+ * csrc/bindings.cpp:35); results follow `linear_attention_decode_reference`
+ * (mega_kernel_qwen36/reference.py:148-166): scalar decay, no beta, equal head counts.
+ *
+ * Layouts: q, k [batch, key_heads, key_dim]; v, out [batch, value_heads, value_dim];
+ * state, new_state [batch, value_heads, key_dim, value_dim] fp32.  value_heads must be a
+ * multiple of key_heads (key head h / (value_heads / key_heads) serves value head h).
+ * new_state may equal state (in-place update); otherwise state is left untouched.
+ * decay_per_head / beta_per_head, when non-NULL, are fp32 [batch, value_heads] and override
+ * the scalar `decay` / a beta of 1.  No workspace is needed.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mk36_linear_attention_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    const float* state;
+    void* out;
+    float* new_state;
+    const float* decay_per_head;
+    const float* beta_per_head;
+    int32_t dtype; /* of q, k, v, out */
+    int32_t batch;
+    int32_t key_heads;
+    int32_t value_heads;
+    int32_t key_dim;
+    int32_t value_dim;
+    float decay;
+} mk36_linear_attention_args;
+
+MK36_API int mk36_linear_attention_decode(const mk36_linear_attention_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MK36_H_ */

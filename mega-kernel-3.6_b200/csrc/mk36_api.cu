@@ -1,0 +1,131 @@
+// Library-level pieces of the C ABI: version, thread-local error text, device info cache,
+// workspace initialisation / status, cooperative launch helper and the bounded-wait self test.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "mk36_common.cuh"
+
+namespace mk36 {
+
+namespace {
+thread_local char g_error[512] = "";
+std::mutex g_info_mutex;
+DeviceInfo g_info[64];
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+const DeviceInfo* current_device_info() {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice failed: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_info_mutex);
+    DeviceInfo& info = g_info[dev];
+    if (info.device == dev) return &info;
+    int sm = 0, smem = 0, coop = 0, major = 0;
+    if ((e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) {
+        set_error("device attribute query failed: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (major != 10) {
+        set_error("this library is built for sm_100a only; device %d has compute capability %d.x", dev, major);
+        return nullptr;
+    }
+    if (!coop) {
+        set_error("device %d does not support cooperative launch", dev);
+        return nullptr;
+    }
+    info.sm_count = sm;
+    info.max_smem_optin = smem;
+    info.cooperative = coop;
+    info.device = dev;
+    return &info;
+}
+
+int launch_cooperative(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       void** params, const char* what) {
+    cudaError_t e = cudaLaunchCooperativeKernel(kernel, grid, block, params, smem, stream);
+    if (e != cudaSuccess) {
+        set_error("%s: cooperative launch failed (grid %u, block %u, smem %zu): %s", what, grid.x, block.x, smem,
+                  cudaGetErrorString(e));
+        return MK36_ERR_LAUNCH;
+    }
+    return MK36_OK;
+}
+
+int max_ctas_per_sm(const void* kernel, int threads, size_t smem) {
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem);
+    if (e != cudaSuccess) {
+        set_error("occupancy query failed: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    return n;
+}
+
+// Two CTAs arrive at a barrier that expects three: the wait is bound to run out.  Exercises
+// the give-up path of the bounded wait without hanging anything.
+__global__ void selftest_wait_kernel(Control* ctl, unsigned long long limit_ns) {
+    if (threadIdx.x == 0) {
+        unsigned gen = barrier_arrive(ctl, gridDim.x + 1);
+        barrier_wait(ctl, gen, kStatusSelfTest, limit_ns);
+    }
+}
+
+}  // namespace mk36
+
+using namespace mk36;
+
+extern "C" {
+
+int mk36_version(void) { return 100; }
+
+const char* mk36_last_error(void) { return g_error; }
+
+size_t mk36_workspace_bytes(void) { return size_t(32) << 20; }
+
+int mk36_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+    if (!workspace) MK36_FAIL(MK36_ERR_WORKSPACE, "workspace is NULL");
+    if (workspace_bytes < kControlBytes) MK36_FAIL(MK36_ERR_WORKSPACE, "workspace smaller than its control block");
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) MK36_FAIL(MK36_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    MK36_CUDA_OK(cudaMemsetAsync(workspace, 0, kControlBytes, static_cast<cudaStream_t>(stream)));
+    return MK36_OK;
+}
+
+int mk36_workspace_status(void* workspace, void* stream, int* device_status) {
+    if (!workspace || !device_status) MK36_FAIL(MK36_ERR_INVALID_ARG, "workspace_status: NULL argument");
+    Control host;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MK36_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(Control), cudaMemcpyDeviceToHost, s));
+    MK36_CUDA_OK(cudaStreamSynchronize(s));
+    *device_status = host.status;
+    if (host.status != 0) MK36_FAIL(MK36_ERR_BARRIER_TIMEOUT, "a bounded device-side wait gave up (code %d)", host.status);
+    return MK36_OK;
+}
+
+// Test hook: runs a two-CTA kernel whose barrier can never complete and whose wait gives up
+// after `limit_ms`.  Afterwards mk36_workspace_status reports MK36_ERR_BARRIER_TIMEOUT and the
+// workspace has to be initialised again.  No counterpart in the reference.
+MK36_API int mk36_selftest_bounded_wait(void* workspace, size_t workspace_bytes, void* stream, int limit_ms) {
+    if (!workspace || workspace_bytes < kControlBytes) MK36_FAIL(MK36_ERR_WORKSPACE, "selftest: bad workspace");
+    if (limit_ms <= 0 || limit_ms > 2000) MK36_FAIL(MK36_ERR_INVALID_ARG, "selftest: limit_ms must be in (0, 2000]");
+    selftest_wait_kernel<<<2, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<Control*>(workspace),
+                                                                      (unsigned long long)limit_ms * 1000000ull);
+    MK36_CUDA_OK(cudaGetLastError());
+    return MK36_OK;
+}
+
+}  // extern "C"

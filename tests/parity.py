@@ -1,0 +1,68 @@
+"""Parity metrics shared by the tests: the tolerances the decode layer is held to.
+
+  * outputs: max-abs <= 2e-2 and relative L2 <= 1e-2 against the CPU oracle on identical inputs;
+  * top-k expert indices: bit-exact;
+  * fp32 recurrent state: relative error <= 1e-4.
+
+One refinement is needed to make "max-abs <= 2e-2" meaningful for bf16 outputs: a bf16 value of
+magnitude >= 4 has a spacing of 2^-5 = 0.031 or more, so two correct fp32 results that differ in
+the last bit but straddle a rounding boundary already differ by more than 2e-2 after rounding.
+The per-element bound is therefore max(2e-2, one unit in the last place of the oracle's value in
+the output dtype); for |value| < 4 in bf16 this is exactly 2e-2.
+"""
+
+from __future__ import annotations
+
+import torch
+
+MAX_ABS = 2e-2
+REL_L2 = 1e-2
+STATE_REL = 1e-4
+
+
+def _ulp(ref: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if dtype == torch.float32:
+        mant = 23
+    elif dtype == torch.float16:
+        mant = 10
+    else:
+        mant = 7
+    mag = ref.abs().double().clamp_min(1e-30)
+    return torch.pow(torch.tensor(2.0, dtype=torch.float64), torch.floor(torch.log2(mag)) - mant)
+
+
+def rel_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    a, e = actual.double().flatten(), expected.double().flatten()
+    denom = float(e.norm())
+    return float((a - e).norm()) / (denom if denom > 0 else 1.0)
+
+
+def max_abs(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    return float((actual.double() - expected.double()).abs().max())
+
+
+def assert_output_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = "output",
+                         max_abs_tol: float = MAX_ABS, rel_l2_tol: float = REL_L2) -> dict:
+    assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} != {tuple(expected.shape)}"
+    a, e = actual.detach().cpu().double(), expected.detach().cpu().double()
+    assert torch.isfinite(a).all(), f"{what}: non-finite values"
+    bound = torch.maximum(torch.full_like(e, max_abs_tol), _ulp(e, actual.dtype))
+    diff = (a - e).abs()
+    worst = float((diff - bound).max())
+    r = rel_l2(a, e)
+    assert worst <= 0.0, f"{what}: max-abs {float(diff.max()):.4g} exceeds bound (worst excess {worst:.3g})"
+    assert r <= rel_l2_tol, f"{what}: rel-L2 {r:.4g} > {rel_l2_tol}"
+    return {"max_abs": float(diff.max()), "rel_l2": r}
+
+
+def assert_state_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = "state", tol: float = STATE_REL) -> float:
+    r = rel_l2(actual.detach().cpu(), expected.detach().cpu())
+    assert r <= tol, f"{what}: relative error {r:.3g} > {tol}"
+    return r
+
+
+def assert_indices_exact(actual: torch.Tensor, expected: torch.Tensor, margin: float | None = None) -> None:
+    a, e = actual.detach().cpu(), expected.detach().cpu()
+    if not torch.equal(a, e):
+        note = f" (smallest logit gap around the cut: {margin:.3g})" if margin is not None else ""
+        raise AssertionError(f"top-k indices differ{note}:\n{a}\nvs\n{e}")
