@@ -1,0 +1,478 @@
+"""Decode-step benchmark of the B200 Qwen3.6 decode layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+
+Headline workload: one MoE decode step of the Qwen3.6-35B-A3B layer shape (hidden 2048, 256
+experts, top-8, expert width 512, one shared expert of width 512), bf16, batch 1, synthetic
+seeded weights ~N(0,0.02) and hidden states ~N(0,1).  One "step" is one pass of the layer over
+one batch.  The metric is microseconds per decode step (lower is better); the roofline object
+reports the achieved HBM bandwidth (algorithmic bytes / step time) against the measured copy peak.
+
+  * `value`      K steps captured in one CUDA graph (inputs resident in HBM), timed with CUDA
+                 events; the steps rotate over several full weight sets whose total size
+                 exceeds the L2, so every step streams from HBM.
+  * `e2e`        the same step through the public operator `mega_kernel_qwen36.moe_decode` with
+                 the hidden state in pinned host memory: host->device copy, kernel, device->host
+                 read of the output inside the timed region.
+  * `cpu_baseline` / `--impl reference`  the CPU oracle (a port of the reference's reference.py)
+                 on the host cores, same workload.
+  * `others`     the remaining decode ops at their measured shapes (MoE batch 8, dense FFN,
+                 32K-context attention, linear attention), same method, reported for context.
+
+With N > 1 (torchrun, one rank per GPU) the MoE runs expert-parallel: every rank holds 256/N
+experts and 1/N of the shared expert, and one NCCL all-reduce of the fp32 partial closes the step
+(strong scaling: the total work is fixed).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "mega-kernel-3.6_b200"))
+
+import torch  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+L2_BYTES = 126 * 1024 * 1024
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (None until a capture of the current kernel exists).
+NCU_TRAFFIC_BYTES = {"moe_b1": None}
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+def time_graph(step_fns, warmup: int, min_region_s: float = 0.0):
+    """Captures the given step callables (one launch each) in one CUDA graph and times one replay
+    with CUDA events on the capture stream.  Returns milliseconds for all steps."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            step_fns[i % len(step_fns)]()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for fn in step_fns:
+                fn()
+        graph.replay()  # untimed replay: graph upload and first-touch effects
+        stream.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        graph.replay()
+        end.record(stream)
+        end.synchronize()
+        return start.elapsed_time(end), graph, stream
+
+
+def build_moe_sets(device, n_sets: int, seed: int = 0):
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    host = syn.moe_weights(syn.MOE_35B_A3B, seed)
+    first = {k: v.to(device) for k, v in host.items()}
+    sets = [mk.MoeWeights(*[first[f] for f in syn.MOE_WEIGHT_FIELDS])]
+    for _ in range(n_sets - 1):
+        sets.append(mk.MoeWeights(*[first[f].clone() for f in syn.MOE_WEIGHT_FIELDS]))
+    return host, sets
+
+
+def distinct_experts(indices: torch.Tensor) -> int:
+    return int(torch.unique(indices).numel())
+
+
+def bench_moe(device, batch: int, steps: int, warmup: int, sets, host_weights, peak):
+    """Graph-timed MoE steps rotating over the weight sets and over different tokens."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    n_tokens = 16
+    xs = [syn.hidden_states(batch, syn.MOE_35B_A3B.hidden, seed=100 + i).to(device) for i in range(n_tokens)]
+    # distinct experts per token set (from an eager run), for the algorithmic byte count
+    uniq = []
+    for x in xs:
+        _, idx, _ = mk.moe_decode(x, sets[0], top_k=8, backend="persistent")
+        uniq.append(distinct_experts(idx))
+    fns = [(lambda i=i: mk.moe_decode(xs[i % n_tokens], sets[i % len(sets)], top_k=8, backend="persistent")) for i in range(steps)]
+    ms, graph, stream = time_graph(fns, warmup)
+    bytes_per_step = statistics.mean(syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, batch, uniq[i % n_tokens]) for i in range(steps))
+    us = ms * 1e3 / steps
+    gbs = bytes_per_step / (us * 1e-6) / 1e9
+    return {"us_per_step": us, "bytes_per_step": bytes_per_step, "achieved_gbs": gbs, "frac_of_measured": gbs / peak,
+            "frac_of_nominal_8tbs": gbs / NOMINAL_HBM_GBS, "distinct_experts_mean": statistics.mean(uniq)}
+
+
+def bench_others(device, steps: int, warmup: int, peak):
+    """Dense FFN, attention and linear attention at their measured shapes (rotating buffers)."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    out = {}
+
+    def record(name, ms, n, nbytes):
+        us = ms * 1e3 / n
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[name] = {"us_per_step": round(us, 3), "bytes_per_step": nbytes, "achieved_gbs": round(gbs, 1),
+                     "frac_of_measured": round(gbs / peak, 4), "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
+
+    # dense FFN 27B: 535 MB of weights per step already exceeds the L2
+    hw = syn.dense_weights(syn.DENSE_27B, 0)
+    dw = mk.DenseFfnWeights(*[hw[f].to(device) for f in syn.DENSE_WEIGHT_FIELDS])
+    n = max(4, min(steps, 20))
+    for batch in (1, 8):
+        x = syn.hidden_states(batch, syn.DENSE_27B.hidden, seed=7).to(device)
+        mk.dense_ffn_decode(x, dw)
+        ms, _, _ = time_graph([lambda: mk.dense_ffn_decode(x, dw)] * n, min(warmup, 3))
+        record(f"dense_ffn_27b_b{batch}", ms, n, syn.dense_algorithmic_bytes(syn.DENSE_27B, batch))
+    del dw, hw
+    torch.cuda.empty_cache()
+
+    # attention: rotate over 4 caches (4 x 64 MiB > L2) at 32K; shorter contexts use more copies
+    for seq in (32768, 4096):
+        copies = max(4, (3 * L2_BYTES) // (2 * seq * 2 * 256 * 2) + 1)
+        t = syn.attention_tensors(1, 16, 2, 256, seq, seed=0)
+        q = t["q"].to(device)
+        caches = [(t["k_cache"].to(device), t["v_cache"].to(device))]
+        for _ in range(copies - 1):
+            caches.append((caches[0][0].clone(), caches[0][1].clone()))
+        ins = [mk.FullAttentionInputs(q=q, k_cache=k, v_cache=v, scale=1.0 / 16) for k, v in caches]
+        mk.full_attention_decode(ins[0])
+        n = max(copies, min(steps, 200))
+        fns = [(lambda i=i: mk.full_attention_decode(ins[i % copies])) for i in range(n)]
+        ms, _, _ = time_graph(fns, warmup)
+        record(f"attention_t{seq}", ms, n, syn.attention_algorithmic_bytes(1, 16, 2, 256, seq))
+        del caches, ins
+        torch.cuda.empty_cache()
+
+    # linear attention: rotate over states totalling > L2 (state is read and written: 2 x 2 MiB x B)
+    for batch in (1, 8):
+        copies = (3 * L2_BYTES) // (batch * 32 * 128 * 128 * 4 * 2) + 2
+        step = next(syn.linear_step_stream(batch, 16, 32, 128, 128, steps=1, seed=0))
+        q, k, v = (step[n_].to(device) for n_ in ("q", "k", "v"))
+        q32, k32 = q.repeat_interleave(2, dim=1).contiguous(), k.repeat_interleave(2, dim=1).contiguous()
+        states = [syn.linear_state(batch, 32, 128, 128, seed=0).to(device)]
+        for _ in range(copies - 1):
+            states.append(states[0].clone())
+        ins = [mk.LinearAttentionInputs(q=q32, k=k32, v=v, state=s, decay=0.9) for s in states]
+        mk.linear_attention_decode(ins[0])
+        n = max(copies, min(steps, 200))
+        fns = [(lambda i=i: mk.linear_attention_decode(ins[i % copies])) for i in range(n)]
+        ms, _, _ = time_graph(fns, warmup)
+        record(f"linear_attention_b{batch}", ms, n, syn.linear_algorithmic_bytes(batch, 16, 32, 128, 128))
+        del states, ins
+        torch.cuda.empty_cache()
+    return out
+
+
+def bench_e2e(device, batch: int, steps: int, warmup: int, sets):
+    """Public operator with host buffers: H2D of the hidden state, kernel, D2H of the output."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    n_tokens = 16
+    host_x = [syn.hidden_states(batch, syn.MOE_35B_A3B.hidden, seed=100 + i).pin_memory() for i in range(n_tokens)]
+    host_out = torch.empty((batch, syn.MOE_35B_A3B.hidden), dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty((batch, syn.MOE_35B_A3B.hidden), dtype=torch.bfloat16, device=device)
+
+    def one(i):
+        x_dev.copy_(host_x[i % n_tokens], non_blocking=True)
+        out, _, _ = mk.moe_decode(x_dev, sets[i % len(sets)], top_k=8, backend="persistent")
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        one(i)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    nbytes = batch * syn.MOE_35B_A3B.hidden * 2
+    return {"value": round(dt / steps * 1e6, 3), "unit": "us", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+
+
+def cpu_oracle_moe(batch: int, budget_s: float, host_weights=None):
+    """The CPU oracle on the same workload, all host threads; returns (us per step, steps, cores)."""
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = host_weights if host_weights is not None else syn.moe_weights(syn.MOE_35B_A3B, 0)
+    ws = [w[f] for f in syn.MOE_WEIGHT_FIELDS]
+    xs = [syn.hidden_states(batch, syn.MOE_35B_A3B.hidden, seed=100 + i) for i in range(16)]
+    for i in range(2):
+        oracle.moe_decode(xs[i], *ws, top_k=8)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    i = 0
+    while (time.perf_counter() < t_end and len(times) < 2000) or len(times) < 5:
+        t0 = time.perf_counter()
+        oracle.moe_decode(xs[i % 16], *ws, top_k=8)
+        times.append(time.perf_counter() - t0)
+        i += 1
+    return statistics.median(times) * 1e6, len(times), cores
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference_arm(ns):
+    """`--impl reference`: the reference's CPU implementation of the path (the oracle port of
+    reference.py; the reference has no compiled CPU code) on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    us, n, cores = cpu_oracle_moe(ns.batch, budget_s=max(5.0, min(60.0, 0.05 * ns.steps)))
+    line = {
+        "impl": "reference",
+        "metric": "us_per_decode_step", "value": round(us, 2), "unit": "us", "n_gpus": ns.gpus, "steps": ns.steps,
+        "warmup": ns.warmup, "ms_per_step": round(us / 1e3, 5), "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(ns.batch, ns.gpus, None),
+        "cpu_baseline": {"value": round(us, 2), "unit": "us", "cores": cores, "kind": "port",
+                         "sample": f"median of {n} steps of the same batch-{ns.batch} MoE workload (torch CPU, {cores} threads)"},
+        "e2e": {"value": round(us, 2), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(batch, gpus, n_sets):
+    cfg = {
+        "workload": f"Qwen3.6-35B-A3B-shape MoE decode layer, batch {batch}: hidden 2048, 256 experts, top-8, expert "
+                    "intermediate 512, shared expert 512, RMSNorm eps 1e-6, residual",
+        "batch": batch,
+        "parallelism": "single GPU" if gpus == 1 else f"expert parallel x{gpus} (256/{gpus} experts + 1/{gpus} of the shared expert per GPU, one fp32 all-reduce)",
+    }
+    if n_sets:
+        cfg["l2"] = f"inputs larger than L2: steps rotate over {n_sets} full weight sets (the step's own bytes x sets > 126 MB) and 16 tokens"
+    return cfg
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--sets", type=int, default=4, help="full weight sets to rotate over")
+    ap.add_argument("--no-others", action="store_true", help="skip the context measurements of the other ops")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ns = ap.parse_args()
+    ns.warmup = max(ns.warmup, 3)
+
+    if ns.impl == "reference":
+        run_reference_arm(ns)
+        return
+
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
+    if not mk.extension_available():
+        raise SystemExit("the sm_100a extension is not built: run `python mega-kernel-3.6_b200/build.py`")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    peak, peak_kind = measured_peak()
+
+    if world > 1:
+        run_expert_parallel(ns, world, rank, device, peak, peak_kind)
+        return
+
+    host_weights, sets = build_moe_sets(device, ns.sets)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    torch.cuda.synchronize()
+    res = bench_moe(device, ns.batch, ns.steps, ns.warmup, sets, host_weights, peak)
+    e2e = bench_e2e(device, ns.batch, ns.steps, ns.warmup, sets)
+    time.sleep(0.25)
+    clocks = sampler.stop()
+
+    others = {}
+    if not ns.no_others:
+        if ns.batch != 8:
+            r8 = bench_moe(device, 8, max(8, ns.steps // 4), ns.warmup, sets, host_weights, peak)
+            others["moe_35b_a3b_b8"] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in r8.items()}
+        del sets
+        torch.cuda.empty_cache()
+        others.update(bench_others(device, ns.steps, ns.warmup, peak))
+
+    cpu = None
+    if not ns.no_cpu:
+        us, n, cores = cpu_oracle_moe(ns.batch, budget_s=10.0, host_weights=host_weights)
+        cpu = {"value": round(us, 2), "unit": "us", "cores": cores, "kind": "port",
+               "sample": f"median of {n} steps of the same batch-{ns.batch} MoE workload (CPU oracle, torch, {cores} threads)"}
+
+    us = res["us_per_step"]
+    line = {
+        "metric": "us_per_decode_step", "value": round(us, 3), "unit": "us", "n_gpus": 1, "steps": ns.steps, "warmup": ns.warmup,
+        "ms_per_step": round(us / 1e3, 6), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(ns.batch, 1, ns.sets),
+        "roofline": {"bound": "hbm", "achieved": round(res["achieved_gbs"], 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(res["frac_of_measured"], 4), "peak_kind": f"of {peak_kind}",
+                     "frac_of_nominal_8tbs": round(res["frac_of_nominal_8tbs"], 4),
+                     "algorithmic_bytes_per_launch": res["bytes_per_step"],
+                     "traffic": NCU_TRAFFIC_BYTES.get(f"moe_b{ns.batch}")},
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": ns.steps, "clocks": clocks, "others": others,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
+    """N ranks, one per GPU: expert-parallel MoE step = local kernel + NCCL all-reduce + residual."""
+    import torch.distributed as dist
+
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import parallel, synthetic as syn
+
+    dist.init_process_group("nccl", device_id=device)
+    host = syn.moe_weights(syn.MOE_35B_A3B, 0)
+    full = mk.MoeWeights(*[host[f] for f in syn.MOE_WEIGHT_FIELDS])
+    shards = []
+    base = parallel.shard_moe_weights(full, rank, world)
+    first = mk.MoeWeights(*[getattr(base.weights, f).to(device) for f in syn.MOE_WEIGHT_FIELDS])
+    shards.append(parallel.MoeShard(first, base.expert_base, rank, world))
+    for _ in range(ns.sets - 1):
+        shards.append(parallel.MoeShard(mk.MoeWeights(*[getattr(first, f).clone() for f in syn.MOE_WEIGHT_FIELDS]),
+                                        base.expert_base, rank, world))
+    del host, full
+    n_tokens = 16
+    xs = [syn.hidden_states(ns.batch, syn.MOE_35B_A3B.hidden, seed=100 + i).to(device) for i in range(n_tokens)]
+
+    def step(i):
+        return parallel.moe_decode_ep(xs[i % n_tokens], shards[i % len(shards)], top_k=8)
+
+    sampler = ClockSampler(device.index)
+    if rank == 0:
+        sampler.start()
+    for i in range(ns.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(ns.steps):
+        step(i)
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([start.elapsed_time(end)], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    e2e = None
+    host_x = [x.cpu().pin_memory() for x in xs]
+    host_out = torch.empty_like(host_x[0]).pin_memory()
+    x_dev = torch.empty_like(xs[0])
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(ns.steps):
+        x_dev.copy_(host_x[i % n_tokens], non_blocking=True)
+        out, _, _ = parallel.moe_decode_ep(x_dev, shards[i % len(shards)], top_k=8)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], device=device)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    nbytes = ns.batch * syn.MOE_35B_A3B.hidden * 2
+    e2e = {"value": round(float(dt) / ns.steps * 1e6, 3), "unit": "us", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+    if rank == 0:
+        clocks = sampler.stop()
+        us = float(ms) * 1e3 / ns.steps
+        nbytes_alg = syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, ns.batch, min(8 * ns.batch, 256))
+        gbs = nbytes_alg / (us * 1e-6) / 1e9
+        line = {
+            "metric": "us_per_decode_step", "value": round(us, 3), "unit": "us", "n_gpus": world, "steps": ns.steps,
+            "warmup": ns.warmup, "ms_per_step": round(us / 1e3, 6), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(ns.batch, world, ns.sets),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak * world, "unit": "GB/s",
+                         "frac": round(gbs / (peak * world), 4), "peak_kind": f"of {peak_kind} x {world} GPUs",
+                         "algorithmic_bytes_per_launch": nbytes_alg, "traffic": None},
+            "cpu_baseline": None, "e2e": e2e, "gpu_launches": ns.steps, "clocks": clocks,
+            "timing": "eager launches (kernel + NCCL all-reduce + residual per step), CUDA events, max over ranks",
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -75,6 +75,12 @@ MK36_API size_t mk36_workspace_bytes(void);
 MK36_API int mk36_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_status);
 
+/* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase
+ * boundaries into the workspace (slot 0 = kernel entry).  This call synchronises `stream` and copies
+ * the first `count` (<= 16) stamps of the last kernel that used the workspace to the HOST array
+ * `stamps`.  The reference has no tracing beyond CUDA-event timers (benchmarks/bench_utils.py:17-56). */
+MK36_API int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stamps, int count);
+
 /* Test hook for the give-up path of the bounded device-side waits: launches two CTAs whose barrier
  * expects a third arrival that never comes; each wait returns after `limit_ms` (1..2000) and
  * records its code in the status word, so that mk36_workspace_status then reports

@@ -116,6 +116,16 @@ int mk36_workspace_status(void* workspace, void* stream, int* device_status) {
     return MK36_OK;
 }
 
+int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stamps, int count) {
+    if (!workspace || !stamps || count <= 0) MK36_FAIL(MK36_ERR_INVALID_ARG, "workspace_trace: bad argument");
+    Control host;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MK36_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(Control), cudaMemcpyDeviceToHost, s));
+    MK36_CUDA_OK(cudaStreamSynchronize(s));
+    for (int i = 0; i < count; ++i) stamps[i] = i < kTraceSlots ? host.trace[i] : 0ull;
+    return MK36_OK;
+}
+
 // Test hook: runs a two-CTA kernel whose barrier can never complete and whose wait gives up
 // after `limit_ms`.  Afterwards mk36_workspace_status reports MK36_ERR_BARRIER_TIMEOUT and the
 // workspace has to be initialised again.  No counterpart in the reference.

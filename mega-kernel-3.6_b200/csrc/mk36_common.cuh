@@ -56,12 +56,17 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // ------------------------------------------------------------------------------------------
 // Workspace control block (first kControlBytes of every workspace)
 // ------------------------------------------------------------------------------------------
+constexpr int kTraceSlots = 16;
+
 struct Control {
     unsigned int bar_count;   // arrivals at the current barrier
     unsigned int bar_gen;     // completed barriers (monotone)
     int status;               // 0 or the code of the wait that gave up
     unsigned int ticket;      // general purpose arrival ticket
-    unsigned int reserved[60];
+    unsigned int reserved[12];
+    // %globaltimer stamps (ns) written by CTA 0 of the last kernel that used this workspace, one
+    // per phase boundary; read back with mk36_workspace_trace
+    unsigned long long trace[kTraceSlots];
 };
 constexpr size_t kControlBytes = 4096;
 static_assert(sizeof(Control) <= kControlBytes, "control block too large");
@@ -86,6 +91,11 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+// Phase stamp for the workspace trace; call from one thread of CTA 0.
+__device__ __forceinline__ void trace_stamp(Control* c, int slot) {
+    if (slot < kTraceSlots) c->trace[slot] = global_timer_ns();
 }
 
 __device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {

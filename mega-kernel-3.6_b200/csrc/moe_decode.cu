@@ -172,6 +172,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     const T* x = static_cast<const T*>(p.x);
     const T* norm_w = static_cast<const T*>(p.norm_w);
 
+    const bool tracer = (cta == 0 && tid == 0);
+    if (tracer) trace_stamp(p.ctl, 0);
+
     // ---------------- phase 0: RMSNorm into shared memory ----------------
     for (int i = tid; i < TB * x_stride; i += kMoeThreads) xs[i] = 0.0f;
     __syncthreads();
@@ -195,6 +198,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     int all_tok[TB];
 #pragma unroll
     for (int t = 0; t < TB; ++t) all_tok[t] = t * x_stride;
+    if (tracer) trace_stamp(p.ctl, 1);
 
     // ---------------- phase A1: router logits ----------------
     unsigned bar_gen = 0;
@@ -213,6 +217,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
         }
         __syncthreads();
         if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+        if (tracer) trace_stamp(p.ctl, 2);
     }
 
     // ---------------- phase A2: shared expert gate/up rows ----------------
@@ -239,9 +244,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     int n_unique = 0;
     if (p.K > 0) {
         // ---------------- wait barrier 1, then select ----------------
+        if (tracer) trace_stamp(p.ctl, 3);
         if (tid == 0) s_flag = barrier_wait(p.ctl, bar_gen, kStatusMoeBarrier1) ? 1 : 0;
         __syncthreads();
         if (!s_flag) return;
+        if (tracer) trace_stamp(p.ctl, 4);
 
         for (int i = tid; i < p.ntok * p.E; i += kMoeThreads) s_logits[i] = __ldcg(p.logits + i);
         for (int i = tid; i < p.E; i += kMoeThreads) s_mask[i] = 0ull;
@@ -322,6 +329,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
         }
         __syncthreads();
         n_unique = s_unique;
+        if (tracer) trace_stamp(p.ctl, 5);
 
         // ---------------- phase B: routed gate/up rows ----------------
         const long long rows_per_expert = 2ll * p.I;
@@ -346,7 +354,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     }
 
     // ---------------- barrier 2 ----------------
+    if (tracer) trace_stamp(p.ctl, 6);
     if (!grid_barrier(p.ctl, ncta, kStatusMoeBarrier2, &s_flag)) return;
+    if (tracer) trace_stamp(p.ctl, 7);
 
     // ---------------- phase C: activations into shared memory ----------------
     // (the shared-memory region that held the normalised tokens is reused)
@@ -375,6 +385,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
             sacts[b * sa_stride + split_index(i, sa_half)] = silu(__ldcg(g + i)) * __ldcg(g + p.Is + i);
     }
     __syncthreads();
+    if (tracer) trace_stamp(p.ctl, 8);
 
     // ---------------- phase C: down projections ----------------
     {
@@ -516,6 +527,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
             }
         }
     }
+    __syncthreads();
+    if (tracer) trace_stamp(p.ctl, 9);
 }
 
 // -------------------------------------------------------------------------------------------

@@ -191,8 +191,10 @@ def linear_step_stream(
     for _ in range(steps):
         q = _normal(rng, (batch, key_heads, key_dim))
         k = _normal(rng, (batch, key_heads, key_dim))
-        q = q / q.norm(dim=-1, keepdim=True)
-        k = k / k.norm(dim=-1, keepdim=True)
+        # normalise in float64 so that the rounded result does not depend on the host's
+        # summation order
+        q = (q.double() / q.double().pow(2).sum(dim=-1, keepdim=True).sqrt()).float()
+        k = (k.double() / k.double().pow(2).sum(dim=-1, keepdim=True).sqrt()).float()
         v = _normal(rng, (batch, value_heads, value_dim))
         g = torch.sigmoid(_normal(rng, (batch, value_heads)))
         beta = torch.sigmoid(_normal(rng, (batch, value_heads)))

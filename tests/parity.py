@@ -55,6 +55,19 @@ def assert_output_parity(actual: torch.Tensor, expected: torch.Tensor, what: str
     return {"max_abs": float(diff.max()), "rel_l2": r}
 
 
+def assert_oracle_matches_fixture(actual: torch.Tensor, fixture: torch.Tensor, what: str) -> None:
+    """The CPU oracle against a stored reference output.  On the machine that made the fixture the
+    two are bit-identical; another CPU may pick different BLAS kernels, so the check allows fp32
+    reassociation noise: 2e-5 absolute (scaled by magnitude) or one unit in the last place of the
+    output dtype, and a relative L2 of 1e-3 (one flipped bf16 rounding in a few thousand values)."""
+    a, e = actual.detach().cpu().double(), fixture.detach().cpu().double()
+    assert a.shape == e.shape, f"{what}: shape mismatch"
+    bound = torch.maximum(2e-5 * e.abs().clamp_min(1.0), _ulp(e, actual.dtype) if actual.dtype != torch.float32 else torch.zeros_like(e))
+    excess = float(((a - e).abs() - bound).max())
+    assert excess <= 0.0, f"{what}: oracle differs from the reference fixture by {float((a - e).abs().max()):.3g}"
+    assert rel_l2(a, e) <= 1e-3, f"{what}: oracle rel-L2 {rel_l2(a, e):.3g} against the reference fixture"
+
+
 def assert_state_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = "state", tol: float = STATE_REL) -> float:
     r = rel_l2(actual.detach().cpu(), expected.detach().cpu())
     assert r <= tol, f"{what}: relative error {r:.3g} > {tol}"

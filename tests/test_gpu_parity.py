@@ -1,0 +1,276 @@
+"""CUDA kernels against the CPU oracle and the reference fixtures, on identical seeded inputs.
+
+Every call goes through the public operators, i.e. through the extension shim and the C ABI of
+libmk36.so.  Tolerances (tests/parity.py): outputs max-abs <= 2e-2 (or one unit in the last
+place of the output dtype where that is larger) and rel-L2 <= 1e-2; top-k indices bit-exact;
+fp32 recurrent state <= 1e-4 relative after each of 64 steps.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from golden_cases import CASES, CASES_BY_NAME
+from parity import assert_indices_exact, assert_output_parity, assert_state_parity, rel_l2
+from runners import assert_same_inputs, build_inputs, golden_state_sample, load_golden, run_cuda, run_oracle
+from test_golden import check_oracle_against_fixture
+
+pytestmark = pytest.mark.gpu
+
+FAST = [c for c in CASES if c.op != "linear"]
+LINEAR = [c for c in CASES if c.op == "linear"]
+
+
+def _margin(case, spec):
+    from oracle import decode_oracle as oracle
+    from mega_kernel_qwen36 import synthetic as syn
+
+    t = spec["tensors"]
+    _, _, _, logits = oracle.moe_decode_f64(t["x"], *[t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=spec["top_k"])
+    return oracle.router_margin(logits, spec["top_k"])
+
+
+@pytest.mark.parametrize("case", FAST, ids=lambda c: c.name)
+def test_kernel_matches_oracle_and_fixture(case, cuda_device):
+    spec = build_inputs(case)
+    golden = load_golden(case.name)
+    assert_same_inputs(case, spec, golden)
+    got = run_cuda(case, spec, cuda_device)
+    ref = run_oracle(case, spec)
+    # the oracle on this host against the stored output of the reference's own reference.py
+    check_oracle_against_fixture(case, ref, golden)
+    if case.op == "moe":
+        if not torch.equal(got["indices"], ref["indices"]):
+            assert_indices_exact(got["indices"], ref["indices"], margin=_margin(case, spec))
+        assert got["indices"].dtype == torch.int64
+        torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(got["weights"].sum(-1), torch.ones(got["weights"].shape[0]), atol=1e-5, rtol=0)
+    assert got["out"].dtype == ref["out"].dtype
+    assert_output_parity(got["out"], ref["out"], what=case.name)
+    assert_output_parity(got["out"], torch.from_numpy(golden["out"]).to(got["out"].dtype), what=case.name + " vs fixture")
+
+
+@pytest.mark.parametrize("case", LINEAR, ids=lambda c: c.name)
+def test_linear_attention_state_drift(case, cuda_device):
+    """64 consecutive steps, feeding the new state back: state error after every step, outputs at
+    every step, and the fixture's final-state sample."""
+    import mega_kernel_qwen36 as mk
+    from oracle import decode_oracle as oracle
+
+    spec = build_inputs(case)
+    golden = load_golden(case.name)
+    assert_same_inputs(case, spec, golden)
+    s_ref = spec["state"]
+    s_gpu = spec["state"].to(cuda_device)
+    s_in_copy = s_gpu.clone()
+    worst = 0.0
+    for si, step in enumerate(spec["steps"]):
+        q = step["q"].repeat_interleave(spec["expand"], dim=1)
+        k = step["k"].repeat_interleave(spec["expand"], dim=1)
+        o_ref, s_ref = oracle.linear_attention_decode(q, k, step["v"], s_ref, decay=spec["decay"])
+        prev = s_gpu
+        o_gpu, s_gpu = mk.linear_attention_decode(mk.LinearAttentionInputs(
+            q=q.to(cuda_device), k=k.to(cuda_device), v=step["v"].to(cuda_device), state=s_gpu, decay=spec["decay"]))
+        if si == 0:
+            assert torch.equal(prev, s_in_copy), "the input state must not be modified"
+            assert s_gpu.data_ptr() != prev.data_ptr()
+        worst = max(worst, assert_state_parity(s_gpu, s_ref, what=f"{case.name} step {si}"))
+        assert_output_parity(o_gpu.cpu(), o_ref, what=f"{case.name} out step {si}")
+    assert s_gpu.dtype == torch.float32
+    # the multiply / add are rounded separately as in the reference, so the state is bit-exact
+    assert torch.equal(s_gpu.cpu(), s_ref), f"state not bit-exact (rel {worst:.3g})"
+    np.testing.assert_array_equal(golden_state_sample(s_gpu), golden["state_sample"])
+
+
+def test_linear_attention_per_head_gates_and_grouped_keys(cuda_device):
+    """16 key heads serving 32 value heads, per-(batch, head) decay g and value scale beta."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    B, HK, HV, DK, DV = 2, 16, 32, 128, 128
+    s_ref = syn.linear_state(B, HV, DK, DV, seed=5)
+    s_gpu = s_ref.to(cuda_device)
+    for si, step in enumerate(syn.linear_step_stream(B, HK, HV, DK, DV, steps=8, seed=5)):
+        o_ref, s_ref = oracle.linear_attention_decode_per_head(step["q"], step["k"], step["v"], s_ref, step["g"], step["beta"])
+        o_gpu, s_gpu = mk.linear_attention_decode_gated(
+            step["q"].to(cuda_device), step["k"].to(cuda_device), step["v"].to(cuda_device), s_gpu,
+            decay_per_head=step["g"].to(cuda_device), beta_per_head=step["beta"].to(cuda_device), inplace=(si % 2 == 1))
+        assert_state_parity(s_gpu, s_ref, what=f"gated step {si}")
+        assert_output_parity(o_gpu.cpu(), o_ref, what=f"gated out step {si}")
+
+
+def test_moe_runs_are_bit_identical(cuda_device):
+    """All reductions have a fixed order: 20 runs give the same bits (a race would not)."""
+    case = CASES_BY_NAME["moe_small_bf16_b3"]
+    spec = build_inputs(case)
+    first = run_cuda(case, spec, cuda_device)
+    for _ in range(19):
+        again = run_cuda(case, spec, cuda_device)
+        assert torch.equal(first["out"], again["out"])
+        assert torch.equal(first["indices"], again["indices"])
+        assert torch.equal(first["weights"], again["weights"])
+
+
+def test_attention_runs_are_bit_identical(cuda_device):
+    case = CASES_BY_NAME["attn_odd_bf16_t777"]
+    spec = build_inputs(case)
+    first = run_cuda(case, spec, cuda_device)
+    for _ in range(9):
+        assert torch.equal(first["out"], run_cuda(case, spec, cuda_device)["out"])
+
+
+def test_moe_without_residual_and_repeated_rows(cuda_device):
+    """add_residual=False, and a batch whose rows are all equal (every token picks the same experts,
+    so one distinct expert serves 8 tokens)."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    t = syn.moe_tensors(syn.MOE_SMALL, 1, seed=3, dtype=torch.bfloat16)
+    t["x"] = t["x"].repeat(8, 1).contiguous()
+    ref, ridx, rw = oracle.moe_decode(t["x"], *[t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=4, add_residual=False)
+    d = {k: v.to(cuda_device) for k, v in t.items()}
+    out, idx, w = mk.moe_decode(d["x"], mk.MoeWeights(*[d[f] for f in syn.MOE_WEIGHT_FIELDS]), top_k=4, add_residual=False)
+    assert_indices_exact(idx, ridx)
+    assert_output_parity(out.cpu(), ref, what="moe no-residual")
+
+
+def test_decode_layer_wiring(cuda_device):
+    """decode_layer = token mixer + residual + FFN with residual, for both layer kinds and both FFNs."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    B, H = 2, 256
+    moe_t = syn.moe_tensors(syn.MOE_SMALL, B, seed=21)
+    dense_t = syn.dense_tensors(syn.DenseShape(256, 704), B, seed=22)
+    hidden = moe_t["x"]
+    attn = syn.attention_tensors(B, 8, 2, 32, 300, seed=23)          # 8 heads x 32 = 256 = hidden
+    lin = {"q": None}
+    step = next(syn.linear_step_stream(B, 4, 4, 64, 64, steps=1, seed=24))  # 4 heads x 64 = 256
+    state = syn.linear_state(B, 4, 64, 64, seed=24)
+    dev = cuda_device
+    moe_w = mk.MoeWeights(*[moe_t[f].to(dev) for f in syn.MOE_WEIGHT_FIELDS])
+    dense_w = mk.DenseFfnWeights(*[dense_t[f].to(dev) for f in syn.DENSE_WEIGHT_FIELDS])
+
+    # layer 3: full attention + MoE
+    r = mk.decode_layer(3, hidden.to(dev), moe_w, top_k=4,
+                        full_attention=mk.FullAttentionInputs(q=attn["q"].to(dev), k_cache=attn["k_cache"].to(dev),
+                                                              v_cache=attn["v_cache"].to(dev)))
+    o = oracle.decode_layer(3, hidden, moe=[moe_t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=4,
+                            full_attention={"q": attn["q"], "k_cache": attn["k_cache"], "v_cache": attn["v_cache"]})
+    assert r.linear_state is None and r.attention_output is not None
+    assert_indices_exact(r.router_indices, o["router_indices"])
+    assert_output_parity(r.hidden.cpu(), o["hidden"], what="layer 3 hidden")
+
+    # layer 0: linear attention + dense FFN
+    r = mk.decode_layer(0, hidden.to(dev), dense_ffn=dense_w,
+                        linear_attention=mk.LinearAttentionInputs(q=step["q"].to(dev), k=step["k"].to(dev),
+                                                                  v=step["v"].to(dev), state=state.to(dev), decay=0.95))
+    o = oracle.decode_layer(0, hidden, dense=[dense_t[f] for f in syn.DENSE_WEIGHT_FIELDS],
+                            linear_attention={"q": step["q"], "k": step["k"], "v": step["v"], "state": state, "decay": 0.95})
+    assert r.router_indices is None and r.linear_state is not None
+    assert_state_parity(r.linear_state, o["linear_state"])
+    assert_output_parity(r.hidden.cpu(), o["hidden"], what="layer 0 hidden")
+
+    with pytest.raises(ValueError, match="full_attention inputs are required"):
+        mk.decode_layer(3, hidden.to(dev), moe_w)
+    with pytest.raises(ValueError, match="either moe or dense_ffn weights are required"):
+        mk.decode_layer(0, hidden.to(dev), linear_attention=mk.LinearAttentionInputs(
+            q=step["q"].to(dev), k=step["k"].to(dev), v=step["v"].to(dev), state=state.to(dev)))
+    del lin
+
+
+def test_attention_with_partial_rope(cuda_device):
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    t = syn.attention_tensors(1, 4, 2, 64, 50, seed=31)
+    ang = torch.linspace(0, 3, 16).repeat(2)
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    q2, k2 = oracle.apply_partial_rope(t["q"], t["k_cache"], cos, sin, 32)
+    ref = oracle.full_attention_decode(q2, k2, t["v_cache"])
+    dev = cuda_device
+    got = mk.full_attention_decode(mk.FullAttentionInputs(q=t["q"].to(dev), k_cache=t["k_cache"].to(dev),
+                                                          v_cache=t["v_cache"].to(dev), cos=cos, sin=sin, rotary_dim=32))
+    assert_output_parity(got.cpu(), ref, what="attention with rope")
+
+
+def test_error_behaviour_on_device(cuda_device):
+    """Same exception types and message fragments as the reference's checks
+    (csrc/persistent_moe_decode.cu:668-696, tests/test_cuda_ops.py:52-65)."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    dev = cuda_device
+    t = {k: v.to(dev) for k, v in syn.moe_tensors(syn.MOE_TINY, 2, seed=7).items()}
+    fields = {f: t[f] for f in syn.MOE_WEIGHT_FIELDS}
+    mixed = dict(fields, expert_gate=fields["expert_gate"].float())
+    with pytest.raises(RuntimeError, match="expert_gate dtype mismatch"):
+        mk.moe_decode(t["x"], mk.MoeWeights(**mixed), top_k=3, backend="persistent")
+    with pytest.raises(RuntimeError, match="top_k must be in"):
+        mk.moe_decode(t["x"], mk.MoeWeights(**fields), top_k=7)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        mk.moe_decode(t["x"].t().contiguous().t(), mk.MoeWeights(**fields), top_k=3)
+    with pytest.raises(RuntimeError, match="state must be float32"):
+        mk.linear_attention_decode(mk.LinearAttentionInputs(
+            q=torch.zeros(1, 2, 4, device=dev), k=torch.zeros(1, 2, 4, device=dev), v=torch.zeros(1, 2, 4, device=dev),
+            state=torch.zeros(1, 2, 4, 4, device=dev, dtype=torch.float16)))
+    with pytest.raises(RuntimeError, match="head_dim > 256"):
+        mk.full_attention_decode(mk.FullAttentionInputs(
+            q=torch.zeros(1, 2, 512, device=dev), k_cache=torch.zeros(1, 4, 2, 512, device=dev),
+            v_cache=torch.zeros(1, 4, 2, 512, device=dev)))
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging(cuda_device):
+    """A barrier that can never complete gives up after its limit and raises the status word; the
+    context stays usable and a re-initialised workspace works again."""
+    import ctypes
+    from mega_kernel_qwen36 import cabi
+
+    lib = cabi.load()
+    nbytes = lib.mk36_workspace_bytes()
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    cabi.check(lib.mk36_workspace_init(ws.data_ptr(), nbytes, stream))
+    status = ctypes.c_int(-1)
+    cabi.check(lib.mk36_workspace_status(ws.data_ptr(), stream, ctypes.byref(status)))
+    assert status.value == 0
+    cabi.check(lib.mk36_selftest_bounded_wait(ws.data_ptr(), nbytes, stream, 50))
+    rc = lib.mk36_workspace_status(ws.data_ptr(), stream, ctypes.byref(status))
+    assert rc == cabi.MK36_ERR_BARRIER_TIMEOUT and status.value == 901
+    assert b"bounded device-side wait" in lib.mk36_last_error()
+    cabi.check(lib.mk36_workspace_init(ws.data_ptr(), nbytes, stream))
+    cabi.check(lib.mk36_workspace_status(ws.data_ptr(), stream, ctypes.byref(status)))
+    assert status.value == 0
+    assert float(torch.ones(4, device=cuda_device).sum()) == 4.0
+
+
+def test_c_abi_direct_call_matches_extension(cuda_device):
+    """The same kernel through ctypes (raw pointers, own workspace) and through the extension."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import cabi, synthetic as syn
+
+    lib = cabi.load()
+    dev = cuda_device
+    t = {k: v.to(dev) for k, v in syn.dense_tensors(syn.DenseShape(256, 704), 3, seed=5).items()}
+    expect = mk.dense_ffn_decode(t["x"], mk.DenseFfnWeights(*[t[f] for f in syn.DENSE_WEIGHT_FIELDS]))
+    out = torch.empty_like(t["x"])
+    args = cabi.DenseFfnArgs(x=t["x"].data_ptr(), norm_weight=t["norm_weight"].data_ptr(), gate_weight=t["gate_weight"].data_ptr(),
+                             up_weight=t["up_weight"].data_ptr(), down_weight=t["down_weight"].data_ptr(), out=out.data_ptr(),
+                             partial_out=None, dtype=cabi.MK36_BF16, batch=3, hidden=256, intermediate=704, add_residual=1, eps=1e-6)
+    nbytes = lib.mk36_workspace_bytes()
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    cabi.check(lib.mk36_workspace_init(ws.data_ptr(), nbytes, stream))
+    cabi.check(lib.mk36_dense_ffn_decode(args, ws.data_ptr(), nbytes, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(out, expect)
+    # argument errors come back as status codes with a message, not as crashes
+    args.hidden = 0
+    assert lib.mk36_dense_ffn_decode(args, ws.data_ptr(), nbytes, stream) == cabi.MK36_ERR_INVALID_ARG
+    assert b"sizes must be positive" in lib.mk36_last_error()
+    args.hidden = 256
+    assert lib.mk36_dense_ffn_decode(args, None, 0, stream) == cabi.MK36_ERR_WORKSPACE
