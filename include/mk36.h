@@ -75,6 +75,11 @@ MK36_API size_t mk36_workspace_bytes(void);
 MK36_API int mk36_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_status);
 
+/* Process-wide switches.  "force_generic" = 1 makes every op use its general register-streaming
+ * kernel even where a specialised shared-memory-ring variant exists (the variants compute the same
+ * function; tests use the switch to cover both).  Unknown names return MK36_ERR_INVALID_ARG. */
+MK36_API int mk36_set_option(const char* name, int value);
+
 /* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase
  * boundaries into the workspace (slot 0 = kernel entry).  This call synchronises `stream` and copies
  * the first `count` (<= 16) stamps of the last kernel that used the workspace to the HOST array

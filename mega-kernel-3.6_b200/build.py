@@ -30,6 +30,7 @@ INCLUDE = ROOT / "include"
 CUDA_SOURCES = [
     "mk36_api.cu",
     "moe_decode.cu",
+    "moe_decode_ring.cu",
     "dense_ffn_decode.cu",
     "attention_decode.cu",
     "linear_attention_decode.cu",

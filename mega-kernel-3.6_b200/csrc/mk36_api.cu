@@ -15,6 +15,11 @@ std::mutex g_info_mutex;
 DeviceInfo g_info[64];
 }  // namespace
 
+Options& options() {
+    static Options o;
+    return o;
+}
+
 void set_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -114,6 +119,15 @@ int mk36_workspace_status(void* workspace, void* stream, int* device_status) {
     *device_status = host.status;
     if (host.status != 0) MK36_FAIL(MK36_ERR_BARRIER_TIMEOUT, "a bounded device-side wait gave up (code %d)", host.status);
     return MK36_OK;
+}
+
+int mk36_set_option(const char* name, int value) {
+    if (!name) MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: name is NULL");
+    if (std::strcmp(name, "force_generic") == 0) {
+        options().force_generic = value ? 1 : 0;
+        return MK36_OK;
+    }
+    MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
 }
 
 int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stamps, int count) {

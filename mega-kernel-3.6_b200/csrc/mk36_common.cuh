@@ -53,6 +53,12 @@ int max_ctas_per_sm(const void* kernel, int threads, size_t smem);
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Process-wide switches set through mk36_set_option (tests use them to reach every code path).
+struct Options {
+    int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
+};
+Options& options();
+
 // ------------------------------------------------------------------------------------------
 // Workspace control block (first kControlBytes of every workspace)
 // ------------------------------------------------------------------------------------------
@@ -74,6 +80,8 @@ static_assert(sizeof(Control) <= kControlBytes, "control block too large");
 // Codes stored in Control::status
 constexpr int kStatusMoeBarrier1 = 101;
 constexpr int kStatusMoeBarrier2 = 102;
+constexpr int kStatusMoeRingProducer = 111;  // producer warp: a stage was never released
+constexpr int kStatusMoeRingConsumer = 112;  // consumer warp: a stage never filled
 constexpr int kStatusDenseBarrier = 201;
 constexpr int kStatusAttnBarrier = 301;
 constexpr int kStatusSelfTest = 901;

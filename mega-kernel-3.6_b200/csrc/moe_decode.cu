@@ -618,9 +618,16 @@ const void* moe_kernel(int dtype, int tb) {
 
 }  // namespace
 
+int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled);
+
 int moe_decode_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int rc = check_moe_args(a);
     if (rc != MK36_OK) return rc;
+    if (!options().force_generic) {
+        bool handled = false;
+        rc = moe_decode_ring_launch(a, workspace, workspace_bytes, stream, &handled);
+        if (rc != MK36_OK || handled) return rc;
+    }
     const DeviceInfo* dev = current_device_info();
     if (!dev) return MK36_ERR_LAUNCH;
     MoePlan plan;

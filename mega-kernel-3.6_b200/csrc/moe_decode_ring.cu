@@ -1,0 +1,773 @@
+// MoE decode, streaming variant for sm_100a (2-byte dtypes, aligned shapes).
+//
+// Same phases and arithmetic as the generic kernel in moe_decode.cu, but the weights do not go
+// through registers on their way from HBM: one producer warp feeds a shared-memory ring with 1-D
+// bulk copies (cp.async.bulk completing on mbarriers, no multicast), sixteen consumer warps drain
+// it.  Because weight addresses depend only on the routing decision, the producer runs ahead of
+// the grid barriers: router rows, shared-expert rows and the CTA's slice of shared_down are
+// requested at kernel entry, before the token is even normalised, and once the top-k is known the
+// routed gate/up rows and then the routed down rows are requested back to back, so the down rows
+// are already in shared memory (or in flight) while the second grid barrier completes.
+//
+//   stream of one CTA:  [router rows][shared gate/up rows] | [routed gate/up rows][routed down rows]
+//                        issued at entry                      issued after the top-k
+//
+// A stage holds whole rows: `rows_h` rows of length hidden for the gate/up/router phases and the
+// CTA's (<= rows_i) output rows of one expert for the down phase.  Stage n is consumed by warp
+// group n % 4; in the row phases each warp of the group takes one row, in the down phase rows
+// wi, wi+4, ...  Partial results per (token, slot) pair are kept apart and summed in slot order at
+// the end, so the result does not depend on timing.
+#include <cfloat>
+#include <climits>
+
+#include "mk36_ring.cuh"
+
+namespace mk36 {
+
+constexpr int kRingConsumerWarps = 16;
+constexpr int kRingConsumerThreads = kRingConsumerWarps * 32;
+constexpr int kRingThreads = kRingConsumerThreads + 32;  // + one producer warp
+constexpr int kRingStageBytes = 16384;
+constexpr int kRingGroups = 4;
+constexpr int kRingGroupWarps = kRingConsumerWarps / kRingGroups;
+constexpr int kRingMaxStages = 12;
+constexpr int kRingMaxTokens = 8;
+constexpr int kRingMaxPairs = 64;
+constexpr int kRingXChunks = 8;  // register-resident token: hidden <= 8 * 32 * 8 = 2048
+
+struct MoeRingParams {
+    const void* x;
+    const void* norm_w;
+    const void* router_w;
+    const void* egate;
+    const void* eup;
+    const void* edown;
+    const void* sgate;
+    const void* sup;
+    const void* sdown;
+    void* out;
+    long long* indices;
+    float* route_w;
+    float* partial_out;
+    Control* ctl;
+    float* logits;  // [ntok][E]
+    float* gu;      // [ntok*K][2][I]
+    float* sgu;     // [ntok][2][Is]
+    int ntok, H, E, K, I, Is;
+    int expert_base, local_experts, add_residual;
+    float eps;
+    int nstages;
+    int rows_h;   // rows of length H per stage
+    int rows_i;   // rows of length I per stage
+    int hr_max;   // max output rows per CTA
+    // byte offsets into dynamic shared memory
+    int off_ring, off_sdown, off_act, off_part, off_logits, off_mask, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
+};
+
+__device__ __forceinline__ int chunks_in(int r0, int r1, int per) { return r1 > r0 ? ((r1 - 1) / per - r0 / per + 1) : 0; }
+
+// rows [first, first + count) of chunk n of the range [r0, r1), chunks aligned to multiples of `per`
+__device__ __forceinline__ void chunk_rows(int r0, int r1, int per, int n, int& first, int& count) {
+    const int m = r0 / per + n;
+    const int a = max(m * per, r0);
+    const int b = min((m + 1) * per, r1);
+    first = a;
+    count = b - a;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack_u4(const uint4& v, float (&f)[8]) {
+    Chunk8<T> c;
+    c.raw = v;
+    unpack8(c, f);
+}
+
+// dot product of one row in shared memory with the register-resident token
+template <typename T>
+__device__ __forceinline__ float row_dot_regs(const T* srow, int Hc, int lane, const float (&xr)[kRingXChunks][8]) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kRingXChunks; ++j) {
+        const int c = lane + 32 * j;
+        if (c < Hc) {
+            float f[8];
+            unpack_u4<T>(lds128(srow + 8 * c), f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(f[i], xr[j][i], acc);
+        }
+    }
+    return warp_sum(acc);
+}
+
+// dot products of one row in shared memory with up to NT tokens kept in shared memory as T
+template <typename T, int NT>
+__device__ __forceinline__ void row_dot_smem(const T* srow, int Hc, int lane, const T* xs, const int (&tok)[NT], int H,
+                                             float (&acc)[NT]) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t] = 0.0f;
+    for (int c = lane; c < Hc; c += 32) {
+        float f[8];
+        unpack_u4<T>(lds128(srow + 8 * c), f);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float g[8];
+            unpack_u4<T>(lds128(xs + (size_t)tok[t] * H + 8 * c), g);
+            float s = acc[t];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(f[i], g[i], s);
+            acc[t] = s;
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t] = warp_sum(acc[t]);
+}
+
+template <typename T, int NT>
+__device__ __forceinline__ void routed_row_smem(const T* srow, const MoeRingParams& p, const T* xs, int Hc, int lane,
+                                                unsigned long long mask, int mat, int i) {
+    int tok[NT], pair[NT];
+    int n = 0;
+    unsigned long long m = mask;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        if (m) {
+            const int bit = __ffsll((long long)m) - 1;
+            m &= m - 1;
+            pair[t] = bit;
+            tok[t] = bit / p.K;
+            n = t + 1;
+        } else {
+            pair[t] = -1;
+            tok[t] = 0;
+        }
+    }
+    float acc[NT];
+    row_dot_smem<T, NT>(srow, Hc, lane, xs, tok, p.H, acc);
+    if (lane == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+            if (t < n) p.gu[((size_t)pair[t] * 2 + mat) * p.I + i] = acc[t];
+    }
+}
+
+// XR: the (single) token lives in registers.
+template <typename T, bool XR>
+__global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const MoeRingParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_flag;
+    __shared__ int s_unique;
+    __shared__ int s_abort;
+    __shared__ float s_red[kRingConsumerWarps];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int ncta = gridDim.x;
+    const int cta = blockIdx.x;
+    const bool is_producer = (warp == kRingConsumerWarps);
+
+    unsigned char* ring = smem + p.off_ring;
+    T* sdown_buf = reinterpret_cast<T*>(smem + p.off_sdown);
+    T* xs = reinterpret_cast<T*>(smem + p.off_act);        // phases A/B: tokens as T [ntok][H]
+    float* acts = reinterpret_cast<float*>(smem + p.off_act);  // phase C: activations (split layout)
+    float* part = reinterpret_cast<float*>(smem + p.off_part);  // [npairs + ntok][hr_max]
+    float* s_logits = reinterpret_cast<float*>(smem + p.off_logits);
+    unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(smem + p.off_mask);
+    int* s_uniq_e = reinterpret_cast<int*>(smem + p.off_uniq_e);
+    unsigned long long* s_uniq_m = reinterpret_cast<unsigned long long*>(smem + p.off_uniq_m);
+    int* s_pair_e = reinterpret_cast<int*>(smem + p.off_pair_e);
+    float* s_pair_w = reinterpret_cast<float*>(smem + p.off_pair_w);
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + p.off_bars);
+    unsigned long long* empty_bar = full_bar + kRingMaxStages;
+    unsigned long long* sdown_bar = empty_bar + kRingMaxStages;
+
+    const T* x = static_cast<const T*>(p.x);
+    const int NS = p.nstages;
+    const int Hc = p.H >> 3;
+    const size_t rowH = (size_t)p.H;  // elements
+
+    // ---- static partition of this CTA's work ----
+    const int r0 = (int)(((long long)p.E * cta) / ncta), r1 = (int)(((long long)p.E * (cta + 1)) / ncta);
+    const int srows = 2 * p.Is;
+    const int s0 = (int)(((long long)srows * cta) / ncta), s1 = (int)(((long long)srows * (cta + 1)) / ncta);
+    const int h0 = (int)(((long long)p.H * cta) / ncta), h1 = (int)(((long long)p.H * (cta + 1)) / ncta);
+    const int hr = h1 - h0;
+    const int nA1 = (p.K > 0) ? chunks_in(r0, r1, p.rows_h) : 0;
+    const int nA2 = chunks_in(s0, s1, p.rows_h);
+    const int nA = nA1 + nA2;  // <= nstages (checked on the host), so phase A never waits for a free stage
+
+    const bool tracer = (cta == 0 && tid == 0);
+    if (tracer) trace_stamp(p.ctl, 0);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kRingMaxStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kRingGroupWarps);
+        }
+        mbar_init(sdown_bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    // =====================================================================================
+    // Producer warp
+    // =====================================================================================
+    if (is_producer) {
+        bool ok = true;
+        // chunk n goes to stage n % NS once the consumers of chunk n - NS have released it
+        auto issue = [&](int n, const T* src, unsigned bytes) {
+            const int stage = n % NS;
+            if (n >= NS) ok = mbar_wait(&empty_bar[stage], ((n / NS) - 1) & 1, &s_abort);
+            if (!ok) return;
+            mbar_arrive_expect_tx(&full_bar[stage], bytes);
+            bulk_copy_g2s(ring + (size_t)stage * kRingStageBytes, src, bytes, &full_bar[stage]);
+        };
+        if (lane == 0) {
+            // shared_down rows of this CTA: needed only in the last phase, requested first
+            if (hr > 0 && p.Is > 0) {
+                const unsigned bytes = (unsigned)((size_t)hr * p.Is * sizeof(T));
+                mbar_arrive_expect_tx(sdown_bar, bytes);
+                bulk_copy_g2s(sdown_buf, static_cast<const T*>(p.sdown) + (size_t)h0 * p.Is, bytes, sdown_bar);
+            }
+            for (int n = 0; n < nA && ok; ++n) {
+                int first, count;
+                const T* src;
+                if (n < nA1) {
+                    chunk_rows(r0, r1, p.rows_h, n, first, count);
+                    src = static_cast<const T*>(p.router_w) + (size_t)first * rowH;
+                } else {
+                    chunk_rows(s0, s1, p.rows_h, n - nA1, first, count);
+                    const int mat = first / p.Is, i = first % p.Is;
+                    src = (mat ? static_cast<const T*>(p.sup) : static_cast<const T*>(p.sgate)) + (size_t)i * rowH;
+                }
+                issue(n, src, (unsigned)((size_t)count * rowH * sizeof(T)));
+            }
+        }
+        __syncthreads();  // (S1) routing is known
+        const int n_unique = s_unique;
+        if (s_abort != 0) ok = false;
+        if (lane == 0 && ok) {
+            const long long rows_per_expert = 2ll * p.I;
+            const long long tasks = rows_per_expert * n_unique;
+            const int t0 = (int)(tasks * cta / ncta), t1 = (int)(tasks * (cta + 1) / ncta);
+            const int nB = chunks_in(t0, t1, p.rows_h);
+            const int cpc = (hr + p.rows_i - 1) / p.rows_i;  // chunks per expert in the down phase
+            const int nC = n_unique * cpc;
+            for (int k = 0; k < nB + nC && ok; ++k) {
+                const int n = nA + k;
+                const T* src;
+                unsigned bytes;
+                if (k < nB) {
+                    int first, count;
+                    chunk_rows(t0, t1, p.rows_h, k, first, count);
+                    const int u = first / (int)rows_per_expert;
+                    const int r = first - u * (int)rows_per_expert;
+                    const int mat = r / p.I, i = r % p.I;
+                    const int e = s_uniq_e[u] - p.expert_base;
+                    src = (mat ? static_cast<const T*>(p.eup) : static_cast<const T*>(p.egate)) + ((size_t)e * p.I + i) * rowH;
+                    bytes = (unsigned)((size_t)count * rowH * sizeof(T));
+                } else {
+                    const int kc = k - nB;
+                    const int u = kc / cpc, part_i = kc % cpc;
+                    const int e = s_uniq_e[u] - p.expert_base;
+                    const int ha = h0 + part_i * p.rows_i;
+                    const int hb = min(h1, ha + p.rows_i);
+                    src = static_cast<const T*>(p.edown) + ((size_t)e * p.H + ha) * p.I;
+                    bytes = (unsigned)((size_t)(hb - ha) * p.I * sizeof(T));
+                }
+                issue(n, src, bytes);
+            }
+        }
+        if (lane == 0 && !ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingProducer);
+        // The consumers wait on every full barrier the producer armed, so all copies into this
+        // CTA's shared memory have landed before the last consumer leaves; nothing more to do.
+        return;
+    }
+
+    // =====================================================================================
+    // Consumer warps
+    // =====================================================================================
+    const int group = warp / kRingGroupWarps;
+    const int wi = warp % kRingGroupWarps;
+
+    // ---- phase 0: RMSNorm of the tokens into shared memory (as T) ----
+    for (int b = 0; b < p.ntok; ++b) {
+        const T* xrow = x + (size_t)b * p.H;
+        float ss = 0.0f;
+        for (int k = tid * 8; k < p.H; k += kRingConsumerThreads * 8) {
+            float f[8];
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + k), f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_red[warp] = ss;
+        named_barrier(1, kRingConsumerThreads);
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kRingConsumerWarps; ++w) tot += s_red[w];
+        const float rstd = 1.0f / sqrtf(tot / (float)p.H + p.eps);
+        for (int k = tid * 8; k < p.H; k += kRingConsumerThreads * 8) {
+            float f[8], g[8];
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + k), f);
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + k), g);
+            T o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = from_float<T>(__fmul_rn(__fmul_rn(f[i], rstd), g[i]));
+            *reinterpret_cast<uint4*>(xs + (size_t)b * p.H + k) = *reinterpret_cast<const uint4*>(o);
+        }
+        named_barrier(1, kRingConsumerThreads);
+    }
+    float xr[kRingXChunks][8];
+    if (XR) {
+#pragma unroll
+        for (int j = 0; j < kRingXChunks; ++j) {
+            const int c = lane + 32 * j;
+            if (c < Hc) {
+                unpack_u4<T>(lds128(xs + 8 * c), xr[j]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xr[j][i] = 0.0f;
+            }
+        }
+    }
+    if (tracer) trace_stamp(p.ctl, 1);
+
+    int all_tok[kRingMaxTokens];
+#pragma unroll
+    for (int t = 0; t < kRingMaxTokens; ++t) all_tok[t] = (t < p.ntok) ? t : 0;
+
+    bool ok = true;
+    // ---- phase A: router rows, then shared gate/up rows ----
+    unsigned bar_gen = 0;
+    // (A warp that has given up keeps walking the loops without touching data, so that every
+    // named barrier below is still reached by all consumer warps.)
+    for (int n = 0; n < nA; ++n) {
+        if (n == nA1 && p.K > 0) {
+            named_barrier(1, kRingConsumerThreads);  // all logits of this CTA are written
+            if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+            if (tracer) trace_stamp(p.ctl, 2);
+        }
+        if (n % kRingGroups != group) continue;
+        const int stage = n % NS;
+        if (ok) ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
+        if (!ok) continue;
+        int first, count;
+        if (n < nA1) chunk_rows(r0, r1, p.rows_h, n, first, count);
+        else chunk_rows(s0, s1, p.rows_h, n - nA1, first, count);
+        for (int j = wi; j < count; j += kRingGroupWarps) {
+            const T* srow = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)j * rowH;
+            const int row = first + j;
+            float acc[kRingMaxTokens];
+            if (XR) {
+                acc[0] = row_dot_regs<T>(srow, Hc, lane, xr);
+            } else {
+                row_dot_smem<T, kRingMaxTokens>(srow, Hc, lane, xs, all_tok, p.H, acc);
+            }
+            if (lane == 0) {
+                for (int t = 0; t < p.ntok; ++t) {
+                    if (n < nA1) p.logits[(size_t)t * p.E + row] = acc[t];
+                    else p.sgu[((size_t)t * 2 + row / p.Is) * p.Is + row % p.Is] = acc[t];
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    if (nA1 == nA && p.K > 0) {  // no shared rows on this CTA: arrive now
+        named_barrier(1, kRingConsumerThreads);
+        if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+        if (tracer) trace_stamp(p.ctl, 2);
+    }
+    if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
+
+    int n_unique = 0;
+    if (p.K > 0) {
+        if (tracer) trace_stamp(p.ctl, 3);
+        if (tid == 0) s_flag = (s_abort == 0 && barrier_wait(p.ctl, bar_gen, kStatusMoeBarrier1)) ? 1 : 0;
+        named_barrier(1, kRingConsumerThreads);
+        if (!s_flag) {
+            if (tid == 0) { s_abort = 1; s_unique = 0; }
+            __syncthreads();  // (S1) releases the producer, which sees the abort flag
+            return;
+        }
+        if (tracer) trace_stamp(p.ctl, 4);
+
+        for (int i = tid; i < p.ntok * p.E; i += kRingConsumerThreads) s_logits[i] = __ldcg(p.logits + i);
+        for (int i = tid; i < p.E; i += kRingConsumerThreads) s_mask[i] = 0ull;
+        named_barrier(1, kRingConsumerThreads);
+
+        for (int b = warp; b < p.ntok; b += kRingConsumerWarps) {
+            float* lg = s_logits + (size_t)b * p.E;
+            float first = 0.0f;
+            for (int r = 0; r < p.K; ++r) {
+                float best = -FLT_MAX;
+                int bi = INT_MAX;
+                for (int e = lane; e < p.E; e += 32) {
+                    const float v = lg[e];
+                    if (v > best) { best = v; bi = e; }
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    const float ov = __shfl_xor_sync(kFullMask, best, off);
+                    const int oi = __shfl_xor_sync(kFullMask, bi, off);
+                    if (oi != INT_MAX && (bi == INT_MAX || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+                }
+                if (bi == INT_MAX) bi = 0;
+                if (r == 0) first = best;
+                if (lane == 0) {
+                    s_pair_e[b * p.K + r] = bi;
+                    s_pair_w[b * p.K + r] = best;
+                    lg[bi] = -FLT_MAX;
+                }
+                __syncwarp();
+            }
+            float partial = 0.0f;
+            for (int r = lane; r < p.K; r += 32) {
+                const float ev = expf(s_pair_w[b * p.K + r] - first);
+                s_pair_w[b * p.K + r] = ev;
+                partial += ev;
+            }
+            const float denom = warp_sum(partial);
+            __syncwarp();
+            for (int r = lane; r < p.K; r += 32) {
+                const float w = s_pair_w[b * p.K + r] / denom;
+                s_pair_w[b * p.K + r] = w;
+                if (cta == 0) {
+                    p.indices[(size_t)b * p.K + r] = (long long)s_pair_e[b * p.K + r];
+                    p.route_w[(size_t)b * p.K + r] = w;
+                }
+            }
+        }
+        named_barrier(1, kRingConsumerThreads);
+        for (int t = tid; t < p.ntok * p.K; t += kRingConsumerThreads) {
+            const int e = s_pair_e[t];
+            if (e >= p.expert_base && e < p.expert_base + p.local_experts) atomicOr(&s_mask[e], 1ull << t);
+        }
+        named_barrier(1, kRingConsumerThreads);
+        if (warp == 0) {
+            int count = 0;
+            for (int base = 0; base < p.E; base += 32) {
+                const int e = base + lane;
+                const unsigned long long m = (e < p.E) ? s_mask[e] : 0ull;
+                const unsigned vote = __ballot_sync(kFullMask, m != 0ull);
+                if (m != 0ull) {
+                    const int pos = count + __popc(vote & ((1u << lane) - 1u));
+                    s_uniq_e[pos] = e;
+                    s_uniq_m[pos] = m;
+                }
+                count += __popc(vote);
+            }
+            if (lane == 0) s_unique = count;
+        }
+    } else if (tid == 0) {
+        s_unique = 0;
+    }
+    __syncthreads();  // (S1) producer starts the routed stream
+    n_unique = s_unique;
+    if (tracer) trace_stamp(p.ctl, 5);
+
+    // ---- phase B: routed gate/up rows ----
+    const long long rows_per_expert = 2ll * p.I;
+    const long long tasks = rows_per_expert * n_unique;
+    const int t0 = (int)(tasks * cta / ncta), t1 = (int)(tasks * (cta + 1) / ncta);
+    const int nB = chunks_in(t0, t1, p.rows_h);
+    for (int k = 0; k < nB && ok; ++k) {
+        const int n = nA + k;
+        if (n % kRingGroups != group) continue;
+        const int stage = n % NS;
+        ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
+        if (!ok) break;  // no named barrier inside this loop, leaving early is safe
+        int first, count;
+        chunk_rows(t0, t1, p.rows_h, k, first, count);
+        for (int j = wi; j < count; j += kRingGroupWarps) {
+            const int task = first + j;
+            const int u = task / (int)rows_per_expert;
+            const int r = task - u * (int)rows_per_expert;
+            const int mat = r / p.I, i = r % p.I;
+            const unsigned long long m = s_uniq_m[u];
+            const T* srow = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)j * rowH;
+            if (XR) {
+                const float acc = row_dot_regs<T>(srow, Hc, lane, xr);
+                if (lane == 0) p.gu[((size_t)(__ffsll((long long)m) - 1) * 2 + mat) * p.I + i] = acc;
+            } else {
+                const int cnt = __popcll(m);
+                if (cnt == 1) routed_row_smem<T, 1>(srow, p, xs, Hc, lane, m, mat, i);
+                else if (cnt == 2) routed_row_smem<T, 2>(srow, p, xs, Hc, lane, m, mat, i);
+                else if (cnt <= 4) routed_row_smem<T, 4>(srow, p, xs, Hc, lane, m, mat, i);
+                else routed_row_smem<T, 8>(srow, p, xs, Hc, lane, m, mat, i);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
+
+    // ---- grid barrier 2: every CTA's gate/up results are in the scratch buffers ----
+    if (tracer) trace_stamp(p.ctl, 6);
+    named_barrier(1, kRingConsumerThreads);
+    if (tid == 0) {
+        bool fine = (s_abort == 0);
+        if (fine) {
+            const unsigned gen = barrier_arrive(p.ctl, ncta);
+            fine = barrier_wait(p.ctl, gen, kStatusMoeBarrier2);
+        }
+        if (!fine) s_abort = 1;
+        s_flag = fine ? 1 : 0;
+    }
+    named_barrier(1, kRingConsumerThreads);
+    if (tracer) trace_stamp(p.ctl, 7);
+    ok = (s_flag != 0);
+
+    // ---- activations into shared memory (the token region is reused) ----
+    const int Ic = p.I >> 3, Isc = p.Is >> 3;
+    const int a_half = Ic * 4, a_stride = Ic * 8;
+    const int sa_half = Isc * 4, sa_stride = Isc * 8;
+    const int npairs = p.ntok * p.K;
+    float* sacts = acts + (size_t)npairs * a_stride;
+    if (ok) {
+        // all (pair, i) elements of the local pairs, flattened so that the loads overlap
+        for (int idx = tid; idx < npairs * p.I; idx += kRingConsumerThreads) {
+            const int pair = idx / p.I, i = idx - pair * p.I;
+            const int e = s_pair_e[pair];
+            if (e >= p.expert_base && e < p.expert_base + p.local_experts) {
+                const float* g = p.gu + (size_t)pair * 2 * p.I;
+                acts[pair * a_stride + split_index(i, a_half)] = silu(__ldcg(g + i)) * __ldcg(g + p.I + i);
+            }
+        }
+        for (int idx = tid; idx < p.ntok * p.Is; idx += kRingConsumerThreads) {
+            const int b = idx / p.Is, i = idx - b * p.Is;
+            const float* g = p.sgu + (size_t)b * 2 * p.Is;
+            sacts[b * sa_stride + split_index(i, sa_half)] = silu(__ldcg(g + i)) * __ldcg(g + p.Is + i);
+        }
+    }
+    named_barrier(1, kRingConsumerThreads);
+    if (tracer) trace_stamp(p.ctl, 8);
+
+    // ---- phase C: down rows.  part[slot][row]: slot < npairs routed pairs, then one per token (shared) ----
+    const int cpc = (hr + p.rows_i - 1) / p.rows_i;
+    const int nC = n_unique * cpc;
+    // shared expert rows from the dedicated buffer: row j -> warp j % 16
+    if (ok && hr > 0 && p.Is > 0) {
+        ok = mbar_wait(sdown_bar, 0, &s_abort);
+        if (ok) {
+            for (int j = warp; j < hr; j += kRingConsumerWarps) {
+                const T* srow = sdown_buf + (size_t)j * p.Is;
+                float acc[kRingMaxTokens];
+#pragma unroll
+                for (int t = 0; t < kRingMaxTokens; ++t) acc[t] = 0.0f;
+                for (int c = lane; c < Isc; c += 32) {
+                    float f[8];
+                    unpack_u4<T>(lds128(srow + 8 * c), f);
+#pragma unroll
+                    for (int t = 0; t < kRingMaxTokens; ++t) {
+                        if (t < p.ntok) {
+                            const float4 a = *reinterpret_cast<const float4*>(sacts + t * sa_stride + 4 * c);
+                            const float4 b = *reinterpret_cast<const float4*>(sacts + t * sa_stride + sa_half + 4 * c);
+                            float s = acc[t];
+                            s = fmaf(f[0], a.x, s); s = fmaf(f[1], a.y, s); s = fmaf(f[2], a.z, s); s = fmaf(f[3], a.w, s);
+                            s = fmaf(f[4], b.x, s); s = fmaf(f[5], b.y, s); s = fmaf(f[6], b.z, s); s = fmaf(f[7], b.w, s);
+                            acc[t] = s;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < kRingMaxTokens; ++t) {
+                    if (t < p.ntok) {
+                        const float v = warp_sum(acc[t]);
+                        if (lane == 0) part[(npairs + t) * p.hr_max + j] = v;
+                    }
+                }
+            }
+        }
+    }
+    for (int k = 0; k < nC && ok; ++k) {
+        const int n = nA + nB + k;
+        if (n % kRingGroups != group) continue;
+        const int stage = n % NS;
+        ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
+        if (!ok) break;
+        const int u = k / cpc, part_i = k % cpc;
+        const int ja = part_i * p.rows_i;
+        const int jb = min(hr, ja + p.rows_i);
+        const unsigned long long mask = s_uniq_m[u];
+        for (int j = ja + wi; j < jb; j += kRingGroupWarps) {
+            const T* srow = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)(j - ja) * p.I;
+            unsigned long long m = mask;
+            while (m) {
+                const int pair = __ffsll((long long)m) - 1;
+                m &= m - 1;
+                float s = 0.0f;
+                for (int c = lane; c < Ic; c += 32) {
+                    float f[8];
+                    unpack_u4<T>(lds128(srow + 8 * c), f);
+                    const float4 a = *reinterpret_cast<const float4*>(acts + pair * a_stride + 4 * c);
+                    const float4 b = *reinterpret_cast<const float4*>(acts + pair * a_stride + a_half + 4 * c);
+                    s = fmaf(f[0], a.x, s); s = fmaf(f[1], a.y, s); s = fmaf(f[2], a.z, s); s = fmaf(f[3], a.w, s);
+                    s = fmaf(f[4], b.x, s); s = fmaf(f[5], b.y, s); s = fmaf(f[6], b.z, s); s = fmaf(f[7], b.w, s);
+                }
+                s = warp_sum(s);
+                if (lane == 0) part[pair * p.hr_max + j] = s;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
+    named_barrier(1, kRingConsumerThreads);
+    if (s_abort != 0) return;
+
+    // ---- combine in slot order, add the residual, round once ----
+    T* out = static_cast<T*>(p.out);
+    for (int idx = tid; idx < p.ntok * hr; idx += kRingConsumerThreads) {
+        const int b = idx / hr, j = idx - b * hr;
+        float v = 0.0f;
+        for (int k = 0; k < p.K; ++k) {
+            const int pair = b * p.K + k;
+            const int e = s_pair_e[pair];
+            if (e >= p.expert_base && e < p.expert_base + p.local_experts) v = fmaf(s_pair_w[pair], part[pair * p.hr_max + j], v);
+        }
+        if (p.Is > 0) v += part[(npairs + b) * p.hr_max + j];
+        const size_t o = (size_t)b * p.H + h0 + j;
+        if (p.partial_out) {
+            p.partial_out[o] = v;
+        } else {
+            if (p.add_residual) v += to_float<T>(x[o]);
+            out[o] = from_float<T>(v);
+        }
+    }
+    if (tracer) trace_stamp(p.ctl, 9);
+}
+
+// -------------------------------------------------------------------------------------------
+// Host side
+// -------------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+const void* ring_kernel_for(bool xr) {
+    return xr ? (const void*)moe_decode_ring_kernel<T, true> : (const void*)moe_decode_ring_kernel<T, false>;
+}
+
+}  // namespace
+
+// Returns MK36_OK after launching, MK36_ERR_UNSUPPORTED (without setting an error) when the
+// shapes do not suit this variant so that the caller can use the generic kernel.
+int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled) {
+    *handled = false;
+    if (a->dtype != MK36_BF16 && a->dtype != MK36_F16) return MK36_OK;
+    const int H = a->hidden, E = a->experts, K = a->top_k, I = a->intermediate, Is = a->shared_intermediate;
+    if (K <= 0 || H % 8 != 0 || I % 8 != 0 || Is % 8 != 0 || I <= 0) return MK36_OK;
+    const int row_h = H * 2, row_i = I * 2;
+    if (row_h > kRingStageBytes || row_i > kRingStageBytes) return MK36_OK;
+    const int rows_h = kRingStageBytes / row_h, rows_i = kRingStageBytes / row_i;
+    // chunk alignment: a stage never straddles two matrices
+    if (I % rows_h != 0 || (Is > 0 && Is % rows_h != 0)) return MK36_OK;
+    const void* ptrs[] = {a->x, a->norm_weight, a->router_weight, a->expert_gate, a->expert_up, a->expert_down,
+                          a->shared_gate, a->shared_up, a->shared_down};
+    for (const void* q : ptrs)
+        if ((reinterpret_cast<uintptr_t>(q) & 15u) != 0) return MK36_OK;
+    const DeviceInfo* dev = current_device_info();
+    if (!dev) return MK36_ERR_LAUNCH;
+    const int ncta = dev->sm_count;
+    const int hr_max = (H + ncta - 1) / ncta;
+    if ((size_t)hr_max * Is * 2 > 32768) return MK36_OK;
+    // phase A must fit in the ring without recycling a stage
+    const int a_rows = (E + ncta - 1) / ncta + 1, s_rows = (2 * Is + ncta - 1) / ncta + 1;
+    const int nA_max = (a_rows + rows_h - 1) / rows_h + 1 + (s_rows + rows_h - 1) / rows_h + 1;
+
+    int tb = kRingMaxTokens;
+    while (tb > 1 && (long long)tb * K > kRingMaxPairs) tb >>= 1;
+    if ((long long)tb * K > kRingMaxPairs) return MK36_OK;
+    if (a->batch < tb) {
+        tb = 1;
+        while (tb < a->batch) tb <<= 1;
+    }
+
+    MoeRingParams p;
+    size_t off = 0;
+    auto take = [&](size_t bytes, size_t align) {
+        off = align_up(off, align);
+        const size_t at = off;
+        off += bytes;
+        return (int)at;
+    };
+    int nstages = 0;
+    for (; tb >= 1; tb >>= 1) {
+        off = 0;
+        const int pairs = tb * K;
+        p.off_sdown = take((size_t)hr_max * Is * 2, 128);
+        const size_t xs_bytes = (size_t)tb * H * 2;
+        const size_t act_bytes = ((size_t)pairs * I + (size_t)tb * Is) * 4;
+        p.off_act = take(xs_bytes > act_bytes ? xs_bytes : act_bytes, 128);
+        p.off_part = take((size_t)(pairs + tb) * hr_max * 4, 16);
+        p.off_logits = take((size_t)tb * E * 4, 16);
+        p.off_mask = take((size_t)E * 8, 16);
+        p.off_uniq_e = take(kRingMaxPairs * 4, 16);
+        p.off_uniq_m = take(kRingMaxPairs * 8, 16);
+        p.off_pair_e = take(kRingMaxPairs * 4, 16);
+        p.off_pair_w = take(kRingMaxPairs * 4, 16);
+        p.off_bars = take((2 * kRingMaxStages + 1) * 8, 16);
+        p.off_ring = take(0, 128);
+        const long long room = (long long)dev->max_smem_optin - (long long)off - 1024;
+        nstages = (int)(room / kRingStageBytes);
+        if (nstages > kRingMaxStages) nstages = kRingMaxStages;
+        if (nstages >= 3 && nstages >= nA_max) break;
+    }
+    if (tb < 1) return MK36_OK;
+    const size_t smem_bytes = (size_t)p.off_ring + (size_t)nstages * kRingStageBytes;
+
+    const size_t scratch = align_up((size_t)tb * E * 4, 256) + align_up((size_t)tb * K * 2 * I * 4, 256) +
+                           align_up((size_t)tb * 2 * (Is > 0 ? Is : 1) * 4, 256);
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        MK36_FAIL(MK36_ERR_WORKSPACE, "moe_decode: workspace is NULL or not 256-byte aligned");
+    if (workspace_bytes < kControlBytes + scratch)
+        MK36_FAIL(MK36_ERR_WORKSPACE, "moe_decode: workspace too small (%zu < %zu bytes)", workspace_bytes, kControlBytes + scratch);
+
+    p.norm_w = a->norm_weight;
+    p.router_w = a->router_weight;
+    p.egate = a->expert_gate;
+    p.eup = a->expert_up;
+    p.edown = a->expert_down;
+    p.sgate = a->shared_gate;
+    p.sup = a->shared_up;
+    p.sdown = a->shared_down;
+    p.ctl = static_cast<Control*>(workspace);
+    unsigned char* sc = static_cast<unsigned char*>(workspace) + kControlBytes;
+    p.logits = reinterpret_cast<float*>(sc);
+    sc += align_up((size_t)tb * E * 4, 256);
+    p.gu = reinterpret_cast<float*>(sc);
+    sc += align_up((size_t)tb * K * 2 * I * 4, 256);
+    p.sgu = reinterpret_cast<float*>(sc);
+    p.H = H; p.E = E; p.K = K; p.I = I; p.Is = Is;
+    p.expert_base = a->expert_base;
+    p.local_experts = a->local_experts;
+    p.add_residual = a->add_residual;
+    p.eps = a->eps;
+    p.nstages = nstages;
+    p.rows_h = rows_h;
+    p.rows_i = rows_i;
+    p.hr_max = hr_max;
+
+    const size_t es = 2;
+    for (int b0 = 0; b0 < a->batch; b0 += tb) {
+        const int ntok = (a->batch - b0 < tb) ? (a->batch - b0) : tb;
+        const bool xr = (ntok == 1 && H <= kRingXChunks * 32 * 8);
+        const void* kernel = (a->dtype == MK36_BF16) ? ring_kernel_for<__nv_bfloat16>(xr) : ring_kernel_for<__half>(xr);
+        MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+        p.ntok = ntok;
+        p.x = static_cast<const unsigned char*>(a->x) + (size_t)b0 * H * es;
+        p.out = a->out ? static_cast<unsigned char*>(a->out) + (size_t)b0 * H * es : nullptr;
+        p.partial_out = a->partial_out ? a->partial_out + (size_t)b0 * H : nullptr;
+        p.indices = reinterpret_cast<long long*>(a->indices) + (size_t)b0 * K;
+        p.route_w = a->route_weights + (size_t)b0 * K;
+        void* params[] = {&p};
+        int rc = launch_cooperative(kernel, dim3(ncta), dim3(kRingThreads), smem_bytes, stream, params, "moe_decode(ring)");
+        if (rc != MK36_OK) return rc;
+    }
+    *handled = true;
+    return MK36_OK;
+}
+
+}  // namespace mk36

@@ -50,6 +50,30 @@ def test_kernel_matches_oracle_and_fixture(case, cuda_device):
     assert_output_parity(got["out"], torch.from_numpy(golden["out"]).to(got["out"].dtype), what=case.name + " vs fixture")
 
 
+GENERIC_PATH_CASES = ["moe_small_bf16_b3", "moe_small_f16_b2", "moe_tiny_bf16_b11", "moe_35b_bf16_b1_s0", "moe_35b_bf16_b8_s0"]
+
+
+@pytest.mark.parametrize("name", GENERIC_PATH_CASES)
+def test_moe_general_kernel_matches_oracle(name, cuda_device):
+    """Shapes that normally take the shared-memory-ring variant, forced through the general
+    register-streaming kernel: both must meet the same tolerances."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    cabi.check(lib.mk36_set_option(b"force_generic", 1))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(b"force_generic", 0))
+    ref = run_oracle(case, spec)
+    assert_indices_exact(got["indices"], ref["indices"])
+    torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+    assert_output_parity(got["out"], ref["out"], what=name + " (general kernel)")
+    assert lib.mk36_set_option(b"no_such_option", 1) == cabi.MK36_ERR_INVALID_ARG
+
+
 @pytest.mark.parametrize("case", LINEAR, ids=lambda c: c.name)
 def test_linear_attention_state_drift(case, cuda_device):
     """64 consecutive steps, feeding the new state back: state error after every step, outputs at
