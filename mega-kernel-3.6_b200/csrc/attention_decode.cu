@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_decode_generic_kernel(
     }
 
     // ---- one grid barrier, then every CTA merges a share of the outputs ----
-    if (!grid_barrier(p.ctl, gridDim.x, kStatusAttnBarrier, &s_flag)) return;
+    if (!grid_barrier(p.ctl, gridDim.x, 0, kStatusAttnBarrier, &s_flag)) return;
+    if (threadIdx.x == 0) barrier_finish(p.ctl, gridDim.x);
 
     const int dchunks = (p.D + 31) / 32;
     const int items = p.B * p.Hq * dchunks;

@@ -85,8 +85,8 @@ int max_ctas_per_sm(const void* kernel, int threads, size_t smem) {
 // the give-up path of the bounded wait without hanging anything.
 __global__ void selftest_wait_kernel(Control* ctl, unsigned long long limit_ns) {
     if (threadIdx.x == 0) {
-        unsigned gen = barrier_arrive(ctl, gridDim.x + 1);
-        barrier_wait(ctl, gen, kStatusSelfTest, limit_ns);
+        const unsigned target = barrier_arrive(ctl, gridDim.x + 1);
+        barrier_wait(ctl, target, kStatusSelfTest, limit_ns);
     }
 }
 
@@ -127,6 +127,10 @@ int mk36_set_option(const char* name, int value) {
         options().force_generic = value ? 1 : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "tlb_warm") == 0) {
+        options().tlb_warm = value ? 1 : 0;
+        return MK36_OK;
+    }
     MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
 }
 
@@ -137,6 +141,15 @@ int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stam
     MK36_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(Control), cudaMemcpyDeviceToHost, s));
     MK36_CUDA_OK(cudaStreamSynchronize(s));
     for (int i = 0; i < count; ++i) stamps[i] = i < kTraceSlots ? host.trace[i] : 0ull;
+    return MK36_OK;
+}
+
+int mk36_workspace_cta_trace(void* workspace, void* stream, unsigned long long* stamps, int ctas) {
+    if (!workspace || !stamps || ctas <= 0 || ctas > kCtaTraceMaxCtas) MK36_FAIL(MK36_ERR_INVALID_ARG, "workspace_cta_trace: bad argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MK36_CUDA_OK(cudaMemcpyAsync(stamps, static_cast<unsigned char*>(workspace) + kCtaTraceOffset,
+                                 (size_t)ctas * kCtaTraceSlots * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+    MK36_CUDA_OK(cudaStreamSynchronize(s));
     return MK36_OK;
 }
 

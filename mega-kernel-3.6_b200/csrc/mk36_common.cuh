@@ -56,6 +56,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Process-wide switches set through mk36_set_option (tests use them to reach every code path).
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
+    int tlb_warm = 1;       // 1: the MoE ring kernel touches every expert slab at entry (page-translation warm-up)
 };
 Options& options();
 
@@ -65,17 +66,24 @@ Options& options();
 constexpr int kTraceSlots = 16;
 
 struct Control {
-    unsigned int bar_count;   // arrivals at the current barrier
-    unsigned int bar_gen;     // completed barriers (monotone)
+    unsigned int bar_count;   // barrier arrivals since the kernel started
+    unsigned int unused0;
     int status;               // 0 or the code of the wait that gave up
-    unsigned int ticket;      // general purpose arrival ticket
+    unsigned int ticket;      // CTAs that have left the kernel (see barrier_finish)
     unsigned int reserved[12];
     // %globaltimer stamps (ns) written by CTA 0 of the last kernel that used this workspace, one
     // per phase boundary; read back with mk36_workspace_trace
     unsigned long long trace[kTraceSlots];
 };
-constexpr size_t kControlBytes = 4096;
-static_assert(sizeof(Control) <= kControlBytes, "control block too large");
+// The control block is followed, inside the first kControlBytes, by per-CTA stamps: thread 0 of
+// CTA c writes slot s at kCtaTraceOffset + (c * kCtaTraceSlots + s) * 8 (read back with
+// mk36_workspace_cta_trace; used to see how far apart the CTAs reach a phase boundary).
+constexpr size_t kCtaTraceOffset = 4096;
+constexpr int kCtaTraceSlots = 4;
+constexpr int kCtaTraceMaxCtas = 384;
+constexpr size_t kControlBytes = 16384;
+static_assert(sizeof(Control) <= kCtaTraceOffset, "control block too large");
+static_assert(kCtaTraceOffset + (size_t)kCtaTraceMaxCtas * kCtaTraceSlots * 8 <= kControlBytes, "per-CTA trace does not fit");
 
 // Codes stored in Control::status
 constexpr int kStatusMoeBarrier1 = 101;
@@ -106,38 +114,47 @@ __device__ __forceinline__ void trace_stamp(Control* c, int slot) {
     if (slot < kTraceSlots) c->trace[slot] = global_timer_ns();
 }
 
+// Per-CTA stamp; call from one thread of each CTA.
+__device__ __forceinline__ void cta_stamp(Control* c, int cta, int slot) {
+    if (cta < kCtaTraceMaxCtas && slot < kCtaTraceSlots) {
+        unsigned long long* base = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(c) + kCtaTraceOffset);
+        base[cta * kCtaTraceSlots + slot] = global_timer_ns();
+    }
+}
+
 __device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
 
-// Split grid barrier.  All CTAs of a co-resident grid call arrive() then wait() the same number
-// of times.  arrive() must be preceded by a __syncthreads() issued by the caller when the CTA's
+// Grid barrier on a counter that only grows during a launch.  Barrier number `ordinal` (0, 1, ...
+// in the order the kernel reaches them) is complete when the counter has reached
+// (ordinal + 1) * nblocks, so the last arrival is visible to the waiters with one atomic and one
+// poll; the counter is put back to zero by the last CTA that leaves the kernel (barrier_finish),
+// which is safe because kernels that share a workspace are ordered by their stream.
+// All CTAs of a co-resident grid call arrive() then wait() for every ordinal, and barrier_finish()
+// once at the end.  arrive() must be preceded by a CTA-wide sync issued by the caller when the CTA's
 // earlier global writes have to be visible to the other CTAs after their wait().
-// Only thread 0 of a CTA touches the counters.
-__device__ __forceinline__ unsigned barrier_arrive(Control* c, unsigned nblocks) {
-    unsigned gen = ld_volatile_u32(&c->bar_gen);
-    __threadfence();
-    unsigned prev = atomicAdd(&c->bar_count, 1u);
-    if (prev == nblocks - 1) {
-        atomicExch(&c->bar_count, 0u);
-        __threadfence();
-        atomicAdd(&c->bar_gen, 1u);
-    }
-    return gen;
+// Only one thread of a CTA touches the counters.  Returns the target for the matching wait.
+__device__ __forceinline__ unsigned barrier_arrive(Control* c, unsigned nblocks, unsigned ordinal = 0) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&c->bar_count) : "memory");
+    return (ordinal + 1u) * nblocks;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 // Returns false when the wait ran out; the status word then holds `code`.
-__device__ __forceinline__ bool barrier_wait(Control* c, unsigned gen, int code,
+__device__ __forceinline__ bool barrier_wait(Control* c, unsigned target, int code,
                                              unsigned long long limit_ns = kWaitLimitNs) {
-    if (ld_volatile_u32(&c->bar_gen) != gen) {
-        __threadfence();
-        return true;
-    }
+    if (ld_acquire_u32(&c->bar_count) >= target) return true;
     const unsigned long long t0 = global_timer_ns();
     unsigned spins = 0;
-    while (ld_volatile_u32(&c->bar_gen) == gen) {
+    while (ld_acquire_u32(&c->bar_count) < target) {
         if ((++spins & 63u) == 0u) {
             if (global_timer_ns() - t0 > limit_ns) {
                 atomicCAS(&c->status, 0, code);
@@ -145,16 +162,26 @@ __device__ __forceinline__ bool barrier_wait(Control* c, unsigned gen, int code,
             }
         }
     }
-    __threadfence();
     return true;
 }
 
+// Called by one thread of every CTA after its last barrier wait: the last CTA to leave resets the
+// counters for the next kernel on this workspace.  CTAs that gave up on a wait do not call it (the
+// workspace then has to be initialised again).
+__device__ __forceinline__ void barrier_finish(Control* c, unsigned nblocks) {
+    if (atomicAdd(&c->ticket, 1u) == nblocks - 1u) {
+        c->bar_count = 0u;
+        c->ticket = 0u;
+        __threadfence();
+    }
+}
+
 // Full barrier for a whole CTA (every thread calls it).  Returns a CTA-uniform flag.
-__device__ __forceinline__ bool grid_barrier(Control* c, unsigned nblocks, int code, int* s_flag) {
+__device__ __forceinline__ bool grid_barrier(Control* c, unsigned nblocks, unsigned ordinal, int code, int* s_flag) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned gen = barrier_arrive(c, nblocks);
-        *s_flag = barrier_wait(c, gen, code) ? 1 : 0;
+        const unsigned target = barrier_arrive(c, nblocks, ordinal);
+        *s_flag = barrier_wait(c, target, code) ? 1 : 0;
     }
     __syncthreads();
     return *s_flag != 0;

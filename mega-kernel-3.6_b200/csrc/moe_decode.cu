@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
             }
         }
         __syncthreads();
-        if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+        if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta, 0);
         if (tracer) trace_stamp(p.ctl, 2);
     }
 
@@ -355,7 +355,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
 
     // ---------------- barrier 2 ----------------
     if (tracer) trace_stamp(p.ctl, 6);
-    if (!grid_barrier(p.ctl, ncta, kStatusMoeBarrier2, &s_flag)) return;
+    if (!grid_barrier(p.ctl, ncta, p.K > 0 ? 1u : 0u, kStatusMoeBarrier2, &s_flag)) return;
+    if (tid == 0) barrier_finish(p.ctl, ncta);
     if (tracer) trace_stamp(p.ctl, 7);
 
     // ---------------- phase C: activations into shared memory ----------------

@@ -2,7 +2,7 @@
 //
 // Same phases and arithmetic as the generic kernel in moe_decode.cu, but the weights do not go
 // through registers on their way from HBM: one producer warp feeds a shared-memory ring with 1-D
-// bulk copies (cp.async.bulk completing on mbarriers, no multicast), sixteen consumer warps drain
+// bulk copies (cp.async.bulk completing on mbarriers, no multicast), twelve consumer warps drain
 // it.  Because weight addresses depend only on the routing decision, the producer runs ahead of
 // the grid barriers: router rows, shared-expert rows and the CTA's slice of shared_down are
 // requested at kernel entry, before the token is even normalised, and once the top-k is known the
@@ -14,7 +14,7 @@
 //
 // A stage holds whole rows: `rows_h` rows of length hidden for the gate/up/router phases and the
 // CTA's (<= rows_i) output rows of one expert for the down phase.  Stage n is consumed by warp
-// group n % 4; in the row phases each warp of the group takes one row, in the down phase rows
+// group n % 3; in the row phases each warp of the group takes one row, in the down phase rows
 // wi, wi+4, ...  Partial results per (token, slot) pair are kept apart and summed in slot order at
 // the end, so the result does not depend on timing.
 #include <cfloat>
@@ -24,16 +24,18 @@
 
 namespace mk36 {
 
-constexpr int kRingConsumerWarps = 16;
+constexpr int kRingConsumerWarps = 12;  // 12 + 1 producer: 13 warps are allocated as 16, i.e. 128 registers per thread
 constexpr int kRingConsumerThreads = kRingConsumerWarps * 32;
 constexpr int kRingThreads = kRingConsumerThreads + 32;  // + one producer warp
 constexpr int kRingStageBytes = 16384;
-constexpr int kRingGroups = 4;
+constexpr int kRingGroups = 3;
 constexpr int kRingGroupWarps = kRingConsumerWarps / kRingGroups;
 constexpr int kRingMaxStages = 12;
 constexpr int kRingMaxTokens = 8;
 constexpr int kRingMaxPairs = 64;
 constexpr int kRingXChunks = 8;  // register-resident token: hidden <= 8 * 32 * 8 = 2048
+constexpr int kTopkPerLane = 8;  // register top-k: experts <= 256
+constexpr int kActBatch = 6;     // 16-byte activation loads in flight per thread
 
 struct MoeRingParams {
     const void* x;
@@ -51,8 +53,8 @@ struct MoeRingParams {
     float* partial_out;
     Control* ctl;
     float* logits;  // [ntok][E]
-    float* gu;      // [ntok*K][2][I]
-    float* sgu;     // [ntok][2][Is]
+    float* gu;      // [ntok*K][I][2]  (gate, up) interleaved
+    float* sgu;     // [ntok][Is][2]
     int ntok, H, E, K, I, Is;
     int expert_base, local_experts, add_residual;
     float eps;
@@ -60,9 +62,14 @@ struct MoeRingParams {
     int rows_h;   // rows of length H per stage
     int rows_i;   // rows of length I per stage
     int hr_max;   // max output rows per CTA
+    int tlb_warm; // 1: touch every expert slab at kernel entry so that its page translation is cached
     // byte offsets into dynamic shared memory
     int off_ring, off_sdown, off_act, off_part, off_logits, off_mask, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
 };
+
+// silu with the hardware exponential and reciprocal (relative error ~1e-6, far inside the output
+// tolerance; the general kernel keeps the accurate form)
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 __device__ __forceinline__ int chunks_in(int r0, int r1, int per) { return r1 > r0 ? ((r1 - 1) / per - r0 / per + 1) : 0; }
 
@@ -146,7 +153,7 @@ __device__ __forceinline__ void routed_row_smem(const T* srow, const MoeRingPara
     if (lane == 0) {
 #pragma unroll
         for (int t = 0; t < NT; ++t)
-            if (t < n) p.gu[((size_t)pair[t] * 2 + mat) * p.I + i] = acc[t];
+            if (t < n) p.gu[((size_t)pair[t] * p.I + i) * 2 + mat] = acc[t];
     }
 }
 
@@ -198,6 +205,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     const bool tracer = (cta == 0 && tid == 0);
     if (tracer) trace_stamp(p.ctl, 0);
+    if (tid == 0) cta_stamp(p.ctl, cta, 3);
 
     if (tid == 0) {
         s_abort = 0;
@@ -223,6 +231,24 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             mbar_arrive_expect_tx(&full_bar[stage], bytes);
             bulk_copy_g2s(ring + (size_t)stage * kRingStageBytes, src, bytes, &full_bar[stage]);
         };
+        if (p.tlb_warm) {
+            // One 32-byte read at both ends of every local expert slab, spread over the grid: the
+            // translations of the pages the routed phases will stream are walked now, while the
+            // router phase runs, instead of at the head of the routed stream.
+            const size_t gu_bytes = (size_t)p.I * p.H * sizeof(T);
+            const int slabs = p.local_experts * 6;
+            unsigned sink = 0;
+            for (int sidx = cta * 32 + lane; sidx < slabs; sidx += ncta * 32) {
+                const int e = sidx / 6, which = sidx % 6;
+                const unsigned char* base = static_cast<const unsigned char*>(which < 2 ? p.egate : (which < 4 ? p.eup : p.edown)) +
+                                            (size_t)e * gu_bytes;
+                const unsigned char* addr = base + ((which & 1) ? gu_bytes - 32 : 0);
+                unsigned v;
+                asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(addr));
+                sink ^= v;
+            }
+            if (sink == 0x9e3779b9u && lane == 33) s_flag = 1;  // never true; keeps the loads alive
+        }
         if (lane == 0) {
             // shared_down rows of this CTA: needed only in the last phase, requested first
             if (hr > 0 && p.Is > 0) {
@@ -292,14 +318,28 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     const int wi = warp % kRingGroupWarps;
 
     // ---- phase 0: RMSNorm of the tokens into shared memory (as T) ----
+    // x and the norm weight are fetched together so that the phase costs one memory round trip.
     for (int b = 0; b < p.ntok; ++b) {
         const T* xrow = x + (size_t)b * p.H;
+        float f[8], g[8];
+        const int k = tid * 8;
+        const bool mine = k < p.H;
+        uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+        if (mine) {
+            xv = *reinterpret_cast<const uint4*>(xrow + k);
+            wv = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + k);
+        }
+        unpack_u4<T>(xv, f);
+        unpack_u4<T>(wv, g);
         float ss = 0.0f;
-        for (int k = tid * 8; k < p.H; k += kRingConsumerThreads * 8) {
-            float f[8];
-            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + k), f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+        for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+        // hidden sizes beyond one pass of the consumer threads
+        for (int kk = k + kRingConsumerThreads * 8; kk < p.H; kk += kRingConsumerThreads * 8) {
+            float e[8];
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + kk), e);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(e[i], e[i], ss);
         }
         ss = warp_sum(ss);
         if (lane == 0) s_red[warp] = ss;
@@ -308,14 +348,20 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 #pragma unroll
         for (int w = 0; w < kRingConsumerWarps; ++w) tot += s_red[w];
         const float rstd = 1.0f / sqrtf(tot / (float)p.H + p.eps);
-        for (int k = tid * 8; k < p.H; k += kRingConsumerThreads * 8) {
-            float f[8], g[8];
-            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + k), f);
-            unpack_u4<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + k), g);
+        if (mine) {
             T o[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = from_float<T>(__fmul_rn(__fmul_rn(f[i], rstd), g[i]));
             *reinterpret_cast<uint4*>(xs + (size_t)b * p.H + k) = *reinterpret_cast<const uint4*>(o);
+        }
+        for (int kk = k + kRingConsumerThreads * 8; kk < p.H; kk += kRingConsumerThreads * 8) {
+            float e[8], h[8];
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(xrow + kk), e);
+            unpack_u4<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + kk), h);
+            T o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = from_float<T>(__fmul_rn(__fmul_rn(e[i], rstd), h[i]));
+            *reinterpret_cast<uint4*>(xs + (size_t)b * p.H + kk) = *reinterpret_cast<const uint4*>(o);
         }
         named_barrier(1, kRingConsumerThreads);
     }
@@ -346,13 +392,14 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     for (int n = 0; n < nA; ++n) {
         if (n == nA1 && p.K > 0) {
             named_barrier(1, kRingConsumerThreads);  // all logits of this CTA are written
-            if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+            if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta, 0);
             if (tracer) trace_stamp(p.ctl, 2);
         }
         if (n % kRingGroups != group) continue;
         const int stage = n % NS;
         if (ok) ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
         if (!ok) continue;
+        if (tracer && n == 0) trace_stamp(p.ctl, 10);
         int first, count;
         if (n < nA1) chunk_rows(r0, r1, p.rows_h, n, first, count);
         else chunk_rows(s0, s1, p.rows_h, n - nA1, first, count);
@@ -368,7 +415,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             if (lane == 0) {
                 for (int t = 0; t < p.ntok; ++t) {
                     if (n < nA1) p.logits[(size_t)t * p.E + row] = acc[t];
-                    else p.sgu[((size_t)t * 2 + row / p.Is) * p.Is + row % p.Is] = acc[t];
+                    else p.sgu[((size_t)t * p.Is + row % p.Is) * 2 + row / p.Is] = acc[t];
                 }
             }
         }
@@ -377,7 +424,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     }
     if (nA1 == nA && p.K > 0) {  // no shared rows on this CTA: arrive now
         named_barrier(1, kRingConsumerThreads);
-        if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta);
+        if (tid == 0) bar_gen = barrier_arrive(p.ctl, ncta, 0);
         if (tracer) trace_stamp(p.ctl, 2);
     }
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
@@ -394,67 +441,133 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
         if (tracer) trace_stamp(p.ctl, 4);
 
-        for (int i = tid; i < p.ntok * p.E; i += kRingConsumerThreads) s_logits[i] = __ldcg(p.logits + i);
-        for (int i = tid; i < p.E; i += kRingConsumerThreads) s_mask[i] = 0ull;
-        named_barrier(1, kRingConsumerThreads);
-
-        for (int b = warp; b < p.ntok; b += kRingConsumerWarps) {
-            float* lg = s_logits + (size_t)b * p.E;
-            float first = 0.0f;
-            for (int r = 0; r < p.K; ++r) {
-                float best = -FLT_MAX;
-                int bi = INT_MAX;
-                for (int e = lane; e < p.E; e += 32) {
-                    const float v = lg[e];
-                    if (v > best) { best = v; bi = e; }
-                }
+        if (p.E <= 32 * kTopkPerLane) {
+            // each lane keeps E/32 logits in registers; a round is two warp reductions
+            for (int b = warp; b < p.ntok; b += kRingConsumerWarps) {
+                float v[kTopkPerLane];
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    const float ov = __shfl_xor_sync(kFullMask, best, off);
-                    const int oi = __shfl_xor_sync(kFullMask, bi, off);
-                    if (oi != INT_MAX && (bi == INT_MAX || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+                for (int j = 0; j < kTopkPerLane; ++j) {
+                    const int e = lane + 32 * j;
+                    v[j] = (e < p.E) ? __ldcg(p.logits + (size_t)b * p.E + e) : -FLT_MAX;
                 }
-                if (bi == INT_MAX) bi = 0;
-                if (r == 0) first = best;
-                if (lane == 0) {
-                    s_pair_e[b * p.K + r] = bi;
-                    s_pair_w[b * p.K + r] = best;
-                    lg[bi] = -FLT_MAX;
+                float first = 0.0f, mine_logit = 0.0f;
+                int mine_e = 0;
+                for (int r = 0; r < p.K; ++r) {
+                    float lb = v[0];
+                    int lj = 0;
+#pragma unroll
+                    for (int j = 1; j < kTopkPerLane; ++j)
+                        if (v[j] > lb) { lb = v[j]; lj = j; }
+                    const unsigned bits = __float_as_uint(lb);
+                    const unsigned key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                    const unsigned kmax = __reduce_max_sync(kFullMask, key);
+                    const unsigned cand = (key == kmax && lb > -FLT_MAX) ? (unsigned)(lane + 32 * lj) : 0xffffffffu;
+                    unsigned win = __reduce_min_sync(kFullMask, cand);
+                    if (win == 0xffffffffu) win = 0;  // fewer finite logits than top_k
+                    const unsigned kb = (kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax;
+                    const float best = __uint_as_float(kb);
+                    if ((int)(win & 31u) == lane) {
+#pragma unroll
+                        for (int j = 0; j < kTopkPerLane; ++j)
+                            if (j == (int)(win >> 5)) v[j] = -FLT_MAX;
+                    }
+                    if (r == 0) first = best;
+                    if ((r & 31) == lane) { mine_logit = best; mine_e = (int)win; }
+                    if ((r & 31) == 31 || r == p.K - 1) {
+                        // flush up to 32 selections: lane l holds selection (r & ~31) + l
+                        const int slot = (r & ~31) + lane;
+                        if (slot <= r) {
+                            s_pair_e[b * p.K + slot] = mine_e;
+                            s_pair_w[b * p.K + slot] = mine_logit;
+                        }
+                    }
                 }
                 __syncwarp();
+                float partial = 0.0f;
+                for (int r = lane; r < p.K; r += 32) {
+                    const float ev = expf(s_pair_w[b * p.K + r] - first);
+                    s_pair_w[b * p.K + r] = ev;
+                    partial += ev;
+                }
+                const float denom = warp_sum(partial);
+                __syncwarp();
+                for (int r = lane; r < p.K; r += 32) {
+                    const float w = s_pair_w[b * p.K + r] / denom;
+                    s_pair_w[b * p.K + r] = w;
+                    if (cta == 0) {
+                        p.indices[(size_t)b * p.K + r] = (long long)s_pair_e[b * p.K + r];
+                        p.route_w[(size_t)b * p.K + r] = w;
+                    }
+                }
             }
-            float partial = 0.0f;
-            for (int r = lane; r < p.K; r += 32) {
-                const float ev = expf(s_pair_w[b * p.K + r] - first);
-                s_pair_w[b * p.K + r] = ev;
-                partial += ev;
-            }
-            const float denom = warp_sum(partial);
-            __syncwarp();
-            for (int r = lane; r < p.K; r += 32) {
-                const float w = s_pair_w[b * p.K + r] / denom;
-                s_pair_w[b * p.K + r] = w;
-                if (cta == 0) {
-                    p.indices[(size_t)b * p.K + r] = (long long)s_pair_e[b * p.K + r];
-                    p.route_w[(size_t)b * p.K + r] = w;
+        } else {
+            for (int i = tid; i < p.ntok * p.E; i += kRingConsumerThreads) s_logits[i] = __ldcg(p.logits + i);
+            named_barrier(1, kRingConsumerThreads);
+            for (int b = warp; b < p.ntok; b += kRingConsumerWarps) {
+                float* lg = s_logits + (size_t)b * p.E;
+                float first = 0.0f;
+                for (int r = 0; r < p.K; ++r) {
+                    float best = -FLT_MAX;
+                    int bi = INT_MAX;
+                    for (int e = lane; e < p.E; e += 32) {
+                        const float v = lg[e];
+                        if (v > best) { best = v; bi = e; }
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) {
+                        const float ov = __shfl_xor_sync(kFullMask, best, off);
+                        const int oi = __shfl_xor_sync(kFullMask, bi, off);
+                        if (oi != INT_MAX && (bi == INT_MAX || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+                    }
+                    if (bi == INT_MAX) bi = 0;
+                    if (r == 0) first = best;
+                    if (lane == 0) {
+                        s_pair_e[b * p.K + r] = bi;
+                        s_pair_w[b * p.K + r] = best;
+                        lg[bi] = -FLT_MAX;
+                    }
+                    __syncwarp();
+                }
+                float partial = 0.0f;
+                for (int r = lane; r < p.K; r += 32) {
+                    const float ev = expf(s_pair_w[b * p.K + r] - first);
+                    s_pair_w[b * p.K + r] = ev;
+                    partial += ev;
+                }
+                const float denom = warp_sum(partial);
+                __syncwarp();
+                for (int r = lane; r < p.K; r += 32) {
+                    const float w = s_pair_w[b * p.K + r] / denom;
+                    s_pair_w[b * p.K + r] = w;
+                    if (cta == 0) {
+                        p.indices[(size_t)b * p.K + r] = (long long)s_pair_e[b * p.K + r];
+                        p.route_w[(size_t)b * p.K + r] = w;
+                    }
                 }
             }
         }
         named_barrier(1, kRingConsumerThreads);
-        for (int t = tid; t < p.ntok * p.K; t += kRingConsumerThreads) {
-            const int e = s_pair_e[t];
-            if (e >= p.expert_base && e < p.expert_base + p.local_experts) atomicOr(&s_mask[e], 1ull << t);
-        }
-        named_barrier(1, kRingConsumerThreads);
+        // group the (token, slot) pairs by distinct local expert: the leader of a group is its
+        // lowest pair index; leaders are listed in pair order
         if (warp == 0) {
+            const int npair = p.ntok * p.K;
             int count = 0;
-            for (int base = 0; base < p.E; base += 32) {
-                const int e = base + lane;
-                const unsigned long long m = (e < p.E) ? s_mask[e] : 0ull;
-                const unsigned vote = __ballot_sync(kFullMask, m != 0ull);
-                if (m != 0ull) {
+            for (int base = 0; base < npair; base += 32) {
+                const int t = base + lane;
+                unsigned long long m = 0ull;
+                bool leader = false;
+                if (t < npair) {
+                    const int e = s_pair_e[t];
+                    if (e >= p.expert_base && e < p.expert_base + p.local_experts) {
+                        for (int q = 0; q < npair; ++q)
+                            if (s_pair_e[q] == e) m |= 1ull << q;
+                        leader = (__ffsll((long long)m) - 1) == t;
+                    }
+                }
+                const unsigned vote = __ballot_sync(kFullMask, leader);
+                if (leader) {
                     const int pos = count + __popc(vote & ((1u << lane) - 1u));
-                    s_uniq_e[pos] = e;
+                    s_uniq_e[pos] = s_pair_e[t];
                     s_uniq_m[pos] = m;
                 }
                 count += __popc(vote);
@@ -479,6 +592,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         const int stage = n % NS;
         ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
         if (!ok) break;  // no named barrier inside this loop, leaving early is safe
+        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 11);
         int first, count;
         chunk_rows(t0, t1, p.rows_h, k, first, count);
         for (int j = wi; j < count; j += kRingGroupWarps) {
@@ -490,7 +604,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             const T* srow = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)j * rowH;
             if (XR) {
                 const float acc = row_dot_regs<T>(srow, Hc, lane, xr);
-                if (lane == 0) p.gu[((size_t)(__ffsll((long long)m) - 1) * 2 + mat) * p.I + i] = acc;
+                if (lane == 0) p.gu[((size_t)(__ffsll((long long)m) - 1) * p.I + i) * 2 + mat] = acc;
             } else {
                 const int cnt = __popcll(m);
                 if (cnt == 1) routed_row_smem<T, 1>(srow, p, xs, Hc, lane, m, mat, i);
@@ -507,17 +621,20 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     // ---- grid barrier 2: every CTA's gate/up results are in the scratch buffers ----
     if (tracer) trace_stamp(p.ctl, 6);
     named_barrier(1, kRingConsumerThreads);
+    if (tid == 0) cta_stamp(p.ctl, cta, 0);
     if (tid == 0) {
         bool fine = (s_abort == 0);
         if (fine) {
-            const unsigned gen = barrier_arrive(p.ctl, ncta);
-            fine = barrier_wait(p.ctl, gen, kStatusMoeBarrier2);
+            const unsigned target = barrier_arrive(p.ctl, ncta, 1);
+            fine = barrier_wait(p.ctl, target, kStatusMoeBarrier2);
+            if (fine) barrier_finish(p.ctl, ncta);
         }
         if (!fine) s_abort = 1;
         s_flag = fine ? 1 : 0;
     }
     named_barrier(1, kRingConsumerThreads);
     if (tracer) trace_stamp(p.ctl, 7);
+    if (tid == 0) cta_stamp(p.ctl, cta, 1);
     ok = (s_flag != 0);
 
     // ---- activations into shared memory (the token region is reused) ----
@@ -527,19 +644,40 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     const int npairs = p.ntok * p.K;
     float* sacts = acts + (size_t)npairs * a_stride;
     if (ok) {
-        // all (pair, i) elements of the local pairs, flattened so that the loads overlap
-        for (int idx = tid; idx < npairs * p.I; idx += kRingConsumerThreads) {
-            const int pair = idx / p.I, i = idx - pair * p.I;
-            const int e = s_pair_e[pair];
-            if (e >= p.expert_base && e < p.expert_base + p.local_experts) {
-                const float* g = p.gu + (size_t)pair * 2 * p.I;
-                acts[pair * a_stride + split_index(i, a_half)] = silu(__ldcg(g + i)) * __ldcg(g + p.I + i);
+        // items: two consecutive i of one (pair | shared token), i.e. one 16-byte (g,u,g,u) load;
+        // a thread issues up to kActBatch loads before it touches the results
+        const int half_i = p.I >> 1, half_is = p.Is >> 1;
+        const int routed_items = npairs * half_i;
+        const int items = routed_items + p.ntok * half_is;
+        for (int base = 0; base < items; base += kRingConsumerThreads * kActBatch) {
+            float4 v[kActBatch];
+            int dst[kActBatch];
+#pragma unroll
+            for (int q = 0; q < kActBatch; ++q) {
+                const int it = base + q * kRingConsumerThreads + tid;
+                dst[q] = -1;
+                v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (it < routed_items) {
+                    const int pair = it / half_i, i = (it - pair * half_i) * 2;
+                    const int e = s_pair_e[pair];
+                    if (e >= p.expert_base && e < p.expert_base + p.local_experts) {
+                        v[q] = __ldcg(reinterpret_cast<const float4*>(p.gu + ((size_t)pair * p.I + i) * 2));
+                        dst[q] = pair * a_stride + split_index(i, a_half);
+                    }
+                } else if (it < items) {
+                    const int r = it - routed_items;
+                    const int b = r / half_is, i = (r - b * half_is) * 2;
+                    v[q] = __ldcg(reinterpret_cast<const float4*>(p.sgu + ((size_t)b * p.Is + i) * 2));
+                    dst[q] = npairs * a_stride + b * sa_stride + split_index(i, sa_half);
+                }
             }
-        }
-        for (int idx = tid; idx < p.ntok * p.Is; idx += kRingConsumerThreads) {
-            const int b = idx / p.Is, i = idx - b * p.Is;
-            const float* g = p.sgu + (size_t)b * 2 * p.Is;
-            sacts[b * sa_stride + split_index(i, sa_half)] = silu(__ldcg(g + i)) * __ldcg(g + p.Is + i);
+#pragma unroll
+            for (int q = 0; q < kActBatch; ++q) {
+                if (dst[q] >= 0) {
+                    acts[dst[q]] = silu_fast(v[q].x) * v[q].y;
+                    acts[dst[q] + 1] = silu_fast(v[q].z) * v[q].w;
+                }
+            }
         }
     }
     named_barrier(1, kRingConsumerThreads);
@@ -582,12 +720,14 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             }
         }
     }
+    if (tracer) trace_stamp(p.ctl, 12);
     for (int k = 0; k < nC && ok; ++k) {
         const int n = nA + nB + k;
         if (n % kRingGroups != group) continue;
         const int stage = n % NS;
         ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
         if (!ok) break;
+        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 13);
         const int u = k / cpc, part_i = k % cpc;
         const int ja = part_i * p.rows_i;
         const int jb = min(hr, ja + p.rows_i);
@@ -614,8 +754,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
+    if (tracer) trace_stamp(p.ctl, 14);
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
     named_barrier(1, kRingConsumerThreads);
+    if (tid == 0) cta_stamp(p.ctl, cta, 2);
     if (s_abort != 0) return;
 
     // ---- combine in slot order, add the residual, round once ----
@@ -749,6 +891,7 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
     p.rows_h = rows_h;
     p.rows_i = rows_i;
     p.hr_max = hr_max;
+    p.tlb_warm = options().tlb_warm;
 
     const size_t es = 2;
     for (int b0 = 0; b0 < a->batch; b0 += tb) {

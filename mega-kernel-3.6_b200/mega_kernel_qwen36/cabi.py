@@ -70,6 +70,7 @@ SIGNATURES = {
     "mk36_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "mk36_set_option": (C.c_int, [C.c_char_p, C.c_int]),
     "mk36_workspace_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_ulonglong), C.c_int]),
+    "mk36_workspace_cta_trace": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_ulonglong), C.c_int]),
     "mk36_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]),
     "mk36_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeArgs)]),
     "mk36_moe_decode": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
