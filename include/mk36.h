@@ -77,14 +77,12 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
 
 /* Process-wide switches.  "force_generic" = 1 makes every op use its general register-streaming
  * kernel even where a specialised shared-memory-ring variant exists (the variants compute the same
- * function; tests use the switch to cover both).  "tlb_warm" (default 1) lets the MoE kernel read 32 bytes
- * at both ends of every expert slab at entry, so that the address translations of the pages the routed
- * phases stream are already cached when routing is known.  Unknown names return MK36_ERR_INVALID_ARG. */
+ * function; tests use the switch to cover both).  Unknown names return MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 
 /* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase
  * boundaries into the workspace (slot 0 = kernel entry).  This call synchronises `stream` and copies
- * the first `count` (<= 16) stamps of the last kernel that used the workspace to the HOST array
+ * the first `count` (<= 24) stamps of the last kernel that used the workspace to the HOST array
  * `stamps`.  The reference has no tracing beyond CUDA-event timers (benchmarks/bench_utils.py:17-56). */
 MK36_API int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stamps, int count);
 

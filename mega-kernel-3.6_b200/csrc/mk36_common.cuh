@@ -56,14 +56,14 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Process-wide switches set through mk36_set_option (tests use them to reach every code path).
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
-    int tlb_warm = 1;       // 1: the MoE ring kernel touches every expert slab at entry (page-translation warm-up)
+    int l2_prefetch = 1;    // 1: ring kernels request their whole stream into L2 ahead of the ring
 };
 Options& options();
 
 // ------------------------------------------------------------------------------------------
 // Workspace control block (first kControlBytes of every workspace)
 // ------------------------------------------------------------------------------------------
-constexpr int kTraceSlots = 16;
+constexpr int kTraceSlots = 24;
 
 struct Control {
     unsigned int bar_count;   // barrier arrivals since the kernel started
