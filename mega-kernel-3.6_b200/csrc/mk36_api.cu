@@ -127,10 +127,6 @@ int mk36_set_option(const char* name, int value) {
         options().force_generic = value ? 1 : 0;
         return MK36_OK;
     }
-    if (std::strcmp(name, "l2_prefetch") == 0) {
-        options().l2_prefetch = value ? 1 : 0;
-        return MK36_OK;
-    }
     MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
 }
 

@@ -53,10 +53,26 @@ int max_ctas_per_sm(const void* kernel, int threads, size_t smem);
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Division by a divisor fixed at launch time: n / d == (n * mul) >> shift for every n < 2^31.
+// (An integer division by a run-time value costs tens of dependent instructions on the GPU; the
+// decode kernels run each code path about once, so such chains are directly visible in their time.)
+struct FastDiv {
+    unsigned d, mul, shift;
+};
+inline FastDiv make_fastdiv(unsigned d) {
+    if (d == 0) d = 1;
+    unsigned s = 0;
+    while ((1ull << s) < d) ++s;
+    FastDiv f;
+    f.d = d;
+    f.mul = (unsigned)(((1ull << (31 + s)) + d - 1) / d);
+    f.shift = 31 + s;
+    return f;
+}
+
 // Process-wide switches set through mk36_set_option (tests use them to reach every code path).
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
-    int l2_prefetch = 1;    // 1: ring kernels request their whole stream into L2 ahead of the ring
 };
 Options& options();
 
@@ -102,6 +118,14 @@ constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
 // Device side
 // ------------------------------------------------------------------------------------------
 constexpr unsigned kFullMask = 0xffffffffu;
+
+__device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
+    return (int)(((unsigned long long)(unsigned)n * f.mul) >> f.shift);
+}
+__device__ __forceinline__ void fdivmod(int n, const FastDiv& f, int& q, int& r) {
+    q = fdiv(n, f);
+    r = n - q * (int)f.d;
+}
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;

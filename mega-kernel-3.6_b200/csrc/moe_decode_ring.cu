@@ -1,24 +1,32 @@
 // MoE decode, streaming variant for sm_100a (2-byte dtypes, aligned shapes).
 //
-// Same phases and arithmetic as the general kernel in moe_decode.cu, but the weights do not go
-// through registers on their way from HBM: one producer warp feeds a shared-memory ring with 1-D
-// bulk copies (cp.async.bulk completing on mbarriers, no multicast) and twelve consumer warps drain
-// it.  Because weight addresses depend only on the routing decision, the producer runs ahead of
-// the grid barriers: router rows, shared-expert rows and the CTA's slice of shared_down are
-// requested at kernel entry, before the token is even normalised, and once the top-k is known the
-// routed gate/up rows and then the routed down rows are requested back to back, so the down rows
-// are already in shared memory (or in flight) while the second grid barrier completes.
+// Same phases and results as the general kernel in moe_decode.cu, organised around two facts
+// measured on B200: a cold HBM access costs 2-3 us, and at batch <= 8 the scalar unpack + FMA
+// work per weight element is as expensive as streaming it.  So
+//   * the weights do not go through registers on their way from HBM: one producer lane feeds a
+//     shared-memory ring of 32 KB stages with 1-D bulk copies (cp.async.bulk completing on
+//     mbarriers, no multicast).  Weight addresses depend only on the routing decision, so the
+//     producer runs ahead of the grid barriers: router rows, shared-expert rows and the CTA's
+//     slice of shared_down are requested at kernel entry, before the token is even normalised,
+//     and once the top-k is known the routed gate/up rows and then the routed down rows are
+//     requested back to back, so the down rows are in shared memory (or in flight) while the
+//     second grid barrier completes;
+//   * the twelve consumer warps contract with the warp-level tensor-core instruction
+//     mma.sync.m16n8k16 (bf16/f16 in, fp32 accumulate): weight rows are the M side (16 rows), the
+//     tokens of the launch are the N side (8 columns), so all tokens are served by the same
+//     instruction stream and one weight byte costs ~1/8 of the instructions of the scalar path.
+//     The normalised token is exactly representable in the activation dtype (the reference rounds
+//     it), so it is an exact MMA operand; fp32 activations of the down projection are split into a
+//     high and a low half (two MMAs) and lose nothing.
 //
 //   stream of one CTA:  [router rows][shared gate+up rows] | [routed gate+up rows][routed down rows]
 //                        issued at entry                      issued after the top-k
 //
-// A stage is 32 KB (bulk copies under 16 KB cost bandwidth on B200).  It holds either
-//   - up to `rows_h` router rows, or
-//   - gate rows i..i+n and, in its second half, up rows i..i+n of one expert (n <= rows_h / 2), so
-//     that one warp forms silu(gate_i . x) * (up_i . x) without a round trip through memory, or
-//   - this CTA's output rows of the down projection of up to `epc` experts.
-// Stage n is consumed by warp group n % 3.  Partial results per (token, slot) pair are kept apart and
-// summed in slot order at the end, so the result does not depend on timing.
+// A stage holds up to `rows_h` router rows, or gate rows i..i+n and (second half) up rows i..i+n
+// of one expert so that silu(gate_i.x) * (up_i.x) is formed without a trip through memory, or this
+// CTA's output rows of the down projection of up to `epc` experts.  Stage n is consumed by warp
+// group n % 3.  Partial results per (token, slot) pair are kept apart and summed in slot order at the
+// end, so the result does not depend on timing.
 #include <cfloat>
 #include <climits>
 
@@ -29,15 +37,16 @@ namespace mk36 {
 constexpr int kRingConsumerWarps = 12;  // 12 + 1 producer: 13 warps are allocated as 16, i.e. 128 registers per thread
 constexpr int kRingConsumerThreads = kRingConsumerWarps * 32;
 constexpr int kRingThreads = kRingConsumerThreads + 32;  // + one producer warp
-constexpr int kRingStageBytes = 32768;
+constexpr int kRingStageBytes = 32768;  // bulk copies under 16 KB cost bandwidth; 32 KB x 3..6 stages streams at the HBM rate
 constexpr int kRingGroups = 3;
 constexpr int kRingGroupWarps = kRingConsumerWarps / kRingGroups;
-constexpr int kRingMaxStages = 6;
-constexpr int kRingMaxTokens = 8;
+constexpr int kRingGroupThreads = kRingGroupWarps * 32;
+constexpr int kRingMaxStages = 6;   // kRingGroups x (1 or 2)
+constexpr int kRingMaxTokens = 8;   // = N of the MMA tile
 constexpr int kRingMaxPairs = 64;
-constexpr int kRingXChunks = 8;  // register-resident token: hidden <= 8 * 32 * 8 = 2048
-constexpr int kTopkPerLane = 8;  // register top-k: experts <= 256
-constexpr int kActBatch = 4;     // 16-byte activation loads in flight per thread
+constexpr int kRingTileRows = 16;   // = M of the MMA tile
+constexpr int kTopkPerLane = 8;     // register top-k: experts <= 256
+constexpr int kActBatch = 4;        // 16-byte activation loads in flight per thread
 
 struct MoeRingParams {
     const void* x;
@@ -61,19 +70,23 @@ struct MoeRingParams {
     int expert_base, local_experts, add_residual;
     float eps;
     int nstages;
-    int rows_h;   // rows of length H per stage (pairs per stage = rows_h / 2)
-    int epc;      // experts per stage in the down phase
-    int hr_max;   // max output rows per CTA
-    int l2_prefetch;  // 1: request the whole routed stream into L2 as soon as routing is known
+    int rows_h;   // rows of length H per stage (<= 16, even; pairs per stage = rows_h / 2)
+    int epc;      // experts per stage in the down phase (<= 4)
+    int hr_max;   // max output rows per CTA (<= 16)
+    int log2_depth;   // stages per consumer group = 1 << log2_depth; nstages = kRingGroups << log2_depth
+    FastDiv fd_ncta, fd_rows_h, fd_pr, fd_I, fd_K, fd_qi, fd_qis, fd_epc;
     // byte offsets into dynamic shared memory
-    int off_ring, off_sdown, off_act, off_part, off_logits, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
+    int off_ring, off_sdown, off_act, off_part, off_red, off_logits, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
 };
 
-__device__ __forceinline__ int chunks_in(int r0, int r1, int per) { return r1 > r0 ? ((r1 - 1) / per - r0 / per + 1) : 0; }
+__device__ __forceinline__ int chunks_in(int r0, int r1, const FastDiv& per) {
+    return r1 > r0 ? (fdiv(r1 - 1, per) - fdiv(r0, per) + 1) : 0;
+}
 
-// items [first, first + count) of chunk n of the range [r0, r1), chunks aligned to multiples of `per`
-__device__ __forceinline__ void chunk_span(int r0, int r1, int per, int n, int& first, int& count) {
-    const int m = r0 / per + n;
+// items [first, first + count) of chunk n of the range [r0, r1), chunks aligned to multiples of `per`;
+// m0 = r0 / per is computed once by the caller
+__device__ __forceinline__ void chunk_span(int r0, int r1, int per, int m0, int n, int& first, int& count) {
+    const int m = m0 + n;
     const int a = max(m * per, r0);
     const int b = min((m + 1) * per, r1);
     first = a;
@@ -87,146 +100,131 @@ __device__ __forceinline__ void unpack_u4(const uint4& v, float (&f)[8]) {
     unpack8(c, f);
 }
 
-// Two rows of shared memory against the register-resident token: independent accumulation chains,
-// interleaved reductions.  With two == false the second row is not read.
+// D += A(16x16, row) * B(16x8, col), fp32 accumulate
 template <typename T>
-__device__ __forceinline__ void row_dot_regs2(const T* srow0, const T* srow1, bool two, int Hc, int lane,
-                                              const float (&xr)[kRingXChunks][8], float& out0, float& out1) {
-    float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < kRingXChunks; ++j) {
-        const int c = lane + 32 * j;
-        if (c < Hc) {
-            float f[8], g[8];
-            unpack_u4<T>(lds128(srow0 + 8 * c), f);
-            unpack_u4<T>(two ? lds128(srow1 + 8 * c) : make_uint4(0, 0, 0, 0), g);
-#pragma unroll
-            for (int i = 0; i < 8; i += 2) {
-                a0 = fmaf(f[i], xr[j][i], a0);
-                a1 = fmaf(f[i + 1], xr[j][i + 1], a1);
-                b0 = fmaf(g[i], xr[j][i], b0);
-                b1 = fmaf(g[i + 1], xr[j][i + 1], b1);
-            }
-        }
-    }
-    float a = a0 + a1, b = b0 + b1;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        a += __shfl_xor_sync(kFullMask, a, off);
-        b += __shfl_xor_sync(kFullMask, b, off);
-    }
-    out0 = a;
-    out1 = b;
+__device__ __forceinline__ void mma_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1);
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                                  unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Two rows of shared memory against NT tokens kept in shared memory as T (token t at xs + tok[t] * H).
-template <typename T, int NT>
-__device__ __forceinline__ void row_dot_smem2(const T* srow0, const T* srow1, bool two, int Hc, int lane, const T* xs,
-                                              const int (&tok)[NT], int H, float (&out0)[NT], float (&out1)[NT]) {
-#pragma unroll
-    for (int t = 0; t < NT; ++t) { out0[t] = 0.0f; out1[t] = 0.0f; }
-    for (int c = lane; c < Hc; c += 32) {
-        float f[8], g[8];
-        unpack_u4<T>(lds128(srow0 + 8 * c), f);
-        unpack_u4<T>(two ? lds128(srow1 + 8 * c) : make_uint4(0, 0, 0, 0), g);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            float xv[8];
-            unpack_u4<T>(lds128(xs + (size_t)tok[t] * H + 8 * c), xv);
-            float s0 = out0[t], s1 = out1[t];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                s0 = fmaf(f[i], xv[i], s0);
-                s1 = fmaf(g[i], xv[i], s1);
-            }
-            out0[t] = s0;
-            out1[t] = s1;
-        }
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            out0[t] += __shfl_xor_sync(kFullMask, out0[t], off);
-            out1[t] += __shfl_xor_sync(kFullMask, out1[t], off);
-        }
-    }
+// One 32-wide slice of the contraction for a 16 x 8 tile.  Lane (g = lane / 4, t = lane % 4) reads
+// the 8 consecutive elements kb + 8t .. kb + 8t + 7 of its rows (A: rows g and g + 8; B: column g)
+// with one 128-bit load each.  The contraction index is permuted the same way on both sides
+// (elements 0,1 | 2,3 feed the first MMA's k slots 2t,2t+1 | 2t+8,2t+9; elements 4,5 | 6,7 the
+// second MMA's), which leaves the sum unchanged and needs no shuffles or ldmatrix.
+template <typename T>
+__device__ __forceinline__ void mma_slice32(float (&d0)[4], float (&d1)[4], const uint4& a_lo, const uint4& a_hi, const uint4& b) {
+    mma_16816<T>(d0, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+    mma_16816<T>(d1, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
 }
 
-// Up to R rows of shared memory (row r at base + r * row_stride elements, r < nrows) against one
-// fp32 activation vector in the split layout; the R chains and reductions are interleaved.
-template <typename T, int R>
-__device__ __forceinline__ void rows_dot_act(const T* base, int row_stride, int nrows, const float* act, int half,
-                                             int nchunks, int lane, float (&out)[R]) {
-    float acc[R];
+__device__ __forceinline__ void add4(float (&d)[4], const float (&s)[4]) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = 0.0f;
-    for (int c = lane; c < nchunks; c += 32) {
-        const float4 a = *reinterpret_cast<const float4*>(act + 4 * c);
-        const float4 b = *reinterpret_cast<const float4*>(act + half + 4 * c);
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (r < nrows) {
-                float f[8];
-                unpack_u4<T>(lds128(base + (size_t)r * row_stride + 8 * c), f);
-                float s = acc[r];
-                s = fmaf(f[0], a.x, s); s = fmaf(f[1], a.y, s); s = fmaf(f[2], a.z, s); s = fmaf(f[3], a.w, s);
-                s = fmaf(f[4], b.x, s); s = fmaf(f[5], b.y, s); s = fmaf(f[6], b.z, s); s = fmaf(f[7], b.w, s);
-                acc[r] = s;
-            }
-        }
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) acc[r] += __shfl_xor_sync(kFullMask, acc[r], off);
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) out[r] = acc[r];
+    for (int i = 0; i < 4; ++i) d[i] += s[i];
 }
 
-// gate row and up row of one intermediate channel against the tokens listed in `mask` (bits =
-// (token, slot) pair indices, or token indices when K == 0): writes silu(g) * u per listed entry.
-template <typename T, int NT>
-__device__ __forceinline__ void pair_rows_smem(const T* grow, const T* urow, int Hc, int H, int lane, const T* xs,
-                                               unsigned long long mask, int K, float* dst, int dst_stride, int i) {
-    int tok[NT], slot[NT];
-    int n = 0;
-    unsigned long long m = mask;
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        if (m) {
-            const int bit = __ffsll((long long)m) - 1;
-            m &= m - 1;
-            slot[t] = bit;
-            tok[t] = K > 0 ? bit / K : bit;
-            n = t + 1;
-        } else {
-            slot[t] = 0;
-            tok[t] = 0;
-        }
+// Tile of `nrows` (<= 16) rows of length `len` (multiple of 32) in shared memory, row r at
+// base + r * row_stride elements, against up to 8 vectors of T in shared memory, vector c at
+// vecs + c * vec_stride (c < ncols).  The warp takes the 32-wide slices kb = 32 * (first + step * i).
+// mma.sync has a latency of tens of cycles on this part, so the sum is spread over four
+// independent accumulators (two slices in flight, two MMAs per slice) and folded at the end.
+template <typename T>
+__device__ __noinline__ void tile_times_vectors(float (&d)[4], const T* base, int row_stride, int nrows, const T* vecs,
+                                                   int vec_stride, int ncols, int len, int first, int step, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const bool row_lo = g < nrows, row_hi = (g + 8) < nrows, col = g < ncols;
+    const T* a_lo = base + (size_t)g * row_stride + 8 * t;
+    const T* a_hi = base + (size_t)(g + 8) * row_stride + 8 * t;
+    const T* b = vecs + (size_t)g * vec_stride + 8 * t;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f}, e2[4] = {0.f, 0.f, 0.f, 0.f}, e3[4] = {0.f, 0.f, 0.f, 0.f};
+    int kb = 32 * first;
+    for (; kb + 32 * step < len; kb += 64 * step) {
+        const int kc = kb + 32 * step;
+        const uint4 va = row_lo ? lds128(a_lo + kb) : zero;
+        const uint4 vb = row_hi ? lds128(a_hi + kb) : zero;
+        const uint4 vx = col ? lds128(b + kb) : zero;
+        const uint4 wa = row_lo ? lds128(a_lo + kc) : zero;
+        const uint4 wb = row_hi ? lds128(a_hi + kc) : zero;
+        const uint4 wx = col ? lds128(b + kc) : zero;
+        mma_slice32<T>(e0, e1, va, vb, vx);
+        mma_slice32<T>(e2, e3, wa, wb, wx);
     }
-    float g[NT], u[NT];
-    row_dot_smem2<T, NT>(grow, urow, true, Hc, lane, xs, tok, H, g, u);
-    if (lane == 0) {
-#pragma unroll
-        for (int t = 0; t < NT; ++t)
-            if (t < n) dst[(size_t)slot[t] * dst_stride + i] = silu(g[t]) * u[t];
+    if (kb < len) {
+        const uint4 va = row_lo ? lds128(a_lo + kb) : zero;
+        const uint4 vb = row_hi ? lds128(a_hi + kb) : zero;
+        const uint4 vx = col ? lds128(b + kb) : zero;
+        mma_slice32<T>(e0, e1, va, vb, vx);
     }
+    add4(e0, e1);
+    add4(e2, e3);
+    add4(e0, e2);
+    add4(d, e0);
+}
+
+// Same with two sets of vectors (high and low halves of fp32 activations) sharing the tile loads.
+// `col_hi` / `col_lo` point at this lane's column (column index = lane / 4) or are null when the
+// column is unused; the whole length is contracted by this warp.  Eight independent accumulators.
+template <typename T>
+__device__ __noinline__ void tile_times_split_vectors(float (&d)[4], const T* base, int row_stride, int nrows,
+                                                         const T* col_hi, const T* col_lo, int len, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const bool row_lo = g < nrows, row_hi = (g + 8) < nrows, col = col_hi != nullptr;
+    const T* a_lo = base + (size_t)g * row_stride + 8 * t;
+    const T* a_hi = base + (size_t)(g + 8) * row_stride + 8 * t;
+    const T* bh = col_hi + 8 * t;
+    const T* bl = col_lo + 8 * t;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    float e[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { e[i][0] = 0.f; e[i][1] = 0.f; e[i][2] = 0.f; e[i][3] = 0.f; }
+    int kb = 0;
+    for (; kb + 32 < len; kb += 64) {
+        const uint4 va = row_lo ? lds128(a_lo + kb) : zero;
+        const uint4 vb = row_hi ? lds128(a_hi + kb) : zero;
+        const uint4 xh = col ? lds128(bh + kb) : zero;
+        const uint4 xl = col ? lds128(bl + kb) : zero;
+        const uint4 wa = row_lo ? lds128(a_lo + kb + 32) : zero;
+        const uint4 wb = row_hi ? lds128(a_hi + kb + 32) : zero;
+        const uint4 yh = col ? lds128(bh + kb + 32) : zero;
+        const uint4 yl = col ? lds128(bl + kb + 32) : zero;
+        mma_slice32<T>(e[0], e[1], va, vb, xh);
+        mma_slice32<T>(e[2], e[3], va, vb, xl);
+        mma_slice32<T>(e[4], e[5], wa, wb, yh);
+        mma_slice32<T>(e[6], e[7], wa, wb, yl);
+    }
+    if (kb < len) {
+        const uint4 va = row_lo ? lds128(a_lo + kb) : zero;
+        const uint4 vb = row_hi ? lds128(a_hi + kb) : zero;
+        const uint4 xh = col ? lds128(bh + kb) : zero;
+        const uint4 xl = col ? lds128(bl + kb) : zero;
+        mma_slice32<T>(e[0], e[1], va, vb, xh);
+        mma_slice32<T>(e[2], e[3], va, vb, xl);
+    }
+    add4(e[0], e[1]); add4(e[2], e[3]); add4(e[4], e[5]); add4(e[6], e[7]);
+    add4(e[0], e[2]); add4(e[4], e[6]);
+    add4(e[0], e[4]);
+    add4(d, e[0]);
+}
+
+// position of the q-th set bit of m (q < popcount(m))
+__device__ __forceinline__ int nth_set_bit(unsigned long long m, int q) {
+    for (int i = 0; i < q; ++i) m &= m - 1;
+    return __ffsll((long long)m) - 1;
 }
 
 template <typename T>
-__device__ __forceinline__ void pair_rows_dispatch(const T* grow, const T* urow, int Hc, int H, int lane, const T* xs,
-                                                   unsigned long long mask, int K, float* dst, int dst_stride, int i) {
-    const int cnt = __popcll(mask);
-    if (cnt == 1) pair_rows_smem<T, 1>(grow, urow, Hc, H, lane, xs, mask, K, dst, dst_stride, i);
-    else if (cnt == 2) pair_rows_smem<T, 2>(grow, urow, Hc, H, lane, xs, mask, K, dst, dst_stride, i);
-    else if (cnt <= 4) pair_rows_smem<T, 4>(grow, urow, Hc, H, lane, xs, mask, K, dst, dst_stride, i);
-    else pair_rows_smem<T, 8>(grow, urow, Hc, H, lane, xs, mask, K, dst, dst_stride, i);
-}
-
-// XR: the (single) token lives in registers.
-template <typename T, bool XR>
 __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const MoeRingParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_flag;
@@ -243,9 +241,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     unsigned char* ring = smem + p.off_ring;
     T* sdown_buf = reinterpret_cast<T*>(smem + p.off_sdown);
-    T* xs = reinterpret_cast<T*>(smem + p.off_act);            // phases A/B: tokens as T [ntok][H]
-    float* acts = reinterpret_cast<float*>(smem + p.off_act);  // phase C: activations (split layout)
-    float* part = reinterpret_cast<float*>(smem + p.off_part); // [npairs + ntok][hr_max]
+    T* xs = reinterpret_cast<T*>(smem + p.off_act);      // phases A/B: tokens as T [ntok][H]
+    T* acts_hi = reinterpret_cast<T*>(smem + p.off_act); // phase C: activations, high halves, then low halves
+    float* part = reinterpret_cast<float*>(smem + p.off_part);  // [npairs + ntok][hr_max]
+    float* red = reinterpret_cast<float*>(smem + p.off_red);    // [groups][2][group warps][16][8]
     float* s_logits = reinterpret_cast<float*>(smem + p.off_logits);
     int* s_uniq_e = reinterpret_cast<int*>(smem + p.off_uniq_e);
     unsigned long long* s_uniq_m = reinterpret_cast<unsigned long long*>(smem + p.off_uniq_m);
@@ -257,19 +256,26 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     const T* x = static_cast<const T*>(p.x);
     const int NS = p.nstages;
-    const int Hc = p.H >> 3;
-    const size_t rowH = (size_t)p.H;       // elements per row of length hidden
-    const int PR = p.rows_h >> 1;          // (gate, up) pairs per stage
+    const size_t rowH = (size_t)p.H;          // elements per row of length hidden
+    const int PR = p.rows_h >> 1;             // (gate, up) pairs per stage
     const size_t up_off = (size_t)PR * rowH;  // element offset of the up rows inside a stage
 
     // ---- static partition of this CTA's work ----
-    const int r0 = (int)(((long long)p.E * cta) / ncta), r1 = (int)(((long long)p.E * (cta + 1)) / ncta);
-    const int s0 = (int)(((long long)p.Is * cta) / ncta), s1 = (int)(((long long)p.Is * (cta + 1)) / ncta);
-    const int h0 = (int)(((long long)p.H * cta) / ncta), h1 = (int)(((long long)p.H * (cta + 1)) / ncta);
+    const int r0 = fdiv(p.E * cta, p.fd_ncta), r1 = fdiv(p.E * (cta + 1), p.fd_ncta);
+    const int s0 = fdiv(p.Is * cta, p.fd_ncta), s1 = fdiv(p.Is * (cta + 1), p.fd_ncta);
+    const int h0 = fdiv(p.H * cta, p.fd_ncta), h1 = fdiv(p.H * (cta + 1), p.fd_ncta);
     const int hr = h1 - h0;
-    const int nA1 = chunks_in(r0, r1, p.rows_h);
-    const int nA2 = chunks_in(s0, s1, PR);
+    const int nA1 = chunks_in(r0, r1, p.fd_rows_h);
+    const int nA2 = chunks_in(s0, s1, p.fd_pr);
     const int nA = nA1 + nA2;
+    const int mA1 = fdiv(r0, p.fd_rows_h), mA2 = fdiv(s0, p.fd_pr);
+    // Chunk n belongs to consumer group n % 3 and lives in one of that group's own stages, so the
+    // barriers of a stage are only ever waited on by one group, which walks its chunks in order and
+    // therefore sees every barrier phase exactly once.  (With stages shared between groups a group
+    // could look at a barrier one phase early and be told that the previous phase is complete.)
+    const int depth_mask = (1 << p.log2_depth) - 1;
+    auto stage_of = [&](int n) { return ((n % kRingGroups) << p.log2_depth) + ((n / kRingGroups) & depth_mask); };
+    auto use_of = [&](int n) { return (n / kRingGroups) >> p.log2_depth; };  // how many times the stage was used before
 
     const bool tracer = (cta == 0 && tid == 0);
     if (tracer) trace_stamp(p.ctl, 0);
@@ -287,75 +293,57 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     __syncthreads();
 
     // =====================================================================================
-    // Producer warp (one lane issues; every copy is at most one stage)
+    // Producer warp.  One lane issues: a bulk copy costs about a quarter of a microsecond to issue
+    // however it is spread over lanes, so the number of copies, not of lanes, is what matters.
     // =====================================================================================
     if (is_producer) {
         bool ok = true;
         // chunk n goes to stage n % NS once the consumers of chunk n - NS have released it
         auto acquire = [&](int n, unsigned bytes) -> unsigned char* {
-            const int stage = n % NS;
-            if (n >= NS) ok = mbar_wait(&empty_bar[stage], ((n / NS) - 1) & 1, &s_abort);
+            const int stage = stage_of(n);
+            if (use_of(n) > 0) ok = mbar_wait(&empty_bar[stage], (use_of(n) - 1) & 1, &s_abort);
             if (!ok) return nullptr;
             mbar_arrive_expect_tx(&full_bar[stage], bytes);
             return ring + (size_t)stage * kRingStageBytes;
         };
         if (lane == 0) {
-            // shared_down rows of this CTA: needed only in the last phase, requested first
+            for (int n = 0; n < nA && ok; ++n) {
+                int first, count;
+                if (n < nA1) {
+                    chunk_span(r0, r1, p.rows_h, mA1, n, first, count);
+                    const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
+                    unsigned char* dst = acquire(n, bytes);
+                    if (dst) bulk_copy_g2s(dst, static_cast<const T*>(p.router_w) + (size_t)first * rowH, bytes, &full_bar[stage_of(n)]);
+                } else {
+                    chunk_span(s0, s1, PR, mA2, n - nA1, first, count);
+                    const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
+                    unsigned char* dst = acquire(n, 2 * bytes);
+                    if (dst) {
+                        bulk_copy_g2s(dst, static_cast<const T*>(p.sgate) + (size_t)first * rowH, bytes, &full_bar[stage_of(n)]);
+                        bulk_copy_g2s(dst + up_off * sizeof(T), static_cast<const T*>(p.sup) + (size_t)first * rowH, bytes, &full_bar[stage_of(n)]);
+                    }
+                }
+            }
+            // shared_down rows of this CTA: needed only in the last phase
             if (hr > 0 && p.Is > 0) {
                 const unsigned bytes = (unsigned)((size_t)hr * p.Is * sizeof(T));
                 mbar_arrive_expect_tx(sdown_bar, bytes);
                 bulk_copy_g2s(sdown_buf, static_cast<const T*>(p.sdown) + (size_t)h0 * p.Is, bytes, sdown_bar);
-            }
-            for (int n = 0; n < nA && ok; ++n) {
-                int first, count;
-                if (n < nA1) {
-                    chunk_span(r0, r1, p.rows_h, n, first, count);
-                    const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
-                    unsigned char* dst = acquire(n, bytes);
-                    if (dst) bulk_copy_g2s(dst, static_cast<const T*>(p.router_w) + (size_t)first * rowH, bytes, &full_bar[n % NS]);
-                } else {
-                    chunk_span(s0, s1, PR, n - nA1, first, count);
-                    const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
-                    unsigned char* dst = acquire(n, 2 * bytes);
-                    if (dst) {
-                        bulk_copy_g2s(dst, static_cast<const T*>(p.sgate) + (size_t)first * rowH, bytes, &full_bar[n % NS]);
-                        bulk_copy_g2s(dst + up_off * sizeof(T), static_cast<const T*>(p.sup) + (size_t)first * rowH, bytes, &full_bar[n % NS]);
-                    }
-                }
             }
         }
         __syncthreads();  // (S1) routing is known
         const int n_unique = s_unique;
         if (s_abort != 0) ok = false;
         if (lane == 0 && ok) {
-            const long long tasks = (long long)p.I * n_unique;
-            const int t0 = (int)(tasks * cta / ncta), t1 = (int)(tasks * (cta + 1) / ncta);
-            const int nB = chunks_in(t0, t1, PR);
-            const int nC = (hr > 0) ? (n_unique + p.epc - 1) / p.epc : 0;
-            // Ask for everything this CTA will stream to be brought into L2 right away: the ring
-            // below can only keep a few stages in flight, and a cold HBM access (with its address
-            // translation) takes microseconds, so without this the later chunks would start their
-            // long trip only when a stage is released.
-            if (p.l2_prefetch) {
-                for (int k = 0; k < nB; ++k) {
-                    int first, count;
-                    chunk_span(t0, t1, PR, k, first, count);
-                    const int u = first / p.I, i = first - u * p.I;
-                    const size_t off = ((size_t)(s_uniq_e[u] - p.expert_base) * p.I + i) * rowH;
-                    const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
-                    bulk_prefetch_l2(static_cast<const T*>(p.egate) + off, bytes);
-                    bulk_prefetch_l2(static_cast<const T*>(p.eup) + off, bytes);
-                }
-                if (hr > 0) {
-                    for (int u = 0; u < n_unique; ++u)
-                        bulk_prefetch_l2(static_cast<const T*>(p.edown) + ((size_t)(s_uniq_e[u] - p.expert_base) * p.H + h0) * p.I,
-                                         (unsigned)((size_t)hr * p.I * sizeof(T)));
-                }
-            }
+            const int tasks = p.I * n_unique;
+            const int t0 = fdiv(tasks * cta, p.fd_ncta), t1 = fdiv(tasks * (cta + 1), p.fd_ncta);
+            const int nB = chunks_in(t0, t1, p.fd_pr);
+            const int mB = fdiv(t0, p.fd_pr);
+            const int nC = (hr > 0) ? fdiv(n_unique + p.epc - 1, p.fd_epc) : 0;
             for (int k = 0; k < nB && ok; ++k) {
-                int first, count;
-                chunk_span(t0, t1, PR, k, first, count);
-                const int u = first / p.I, i = first - u * p.I;
+                int first, count, u, i;
+                chunk_span(t0, t1, PR, mB, k, first, count);
+                fdivmod(first, p.fd_I, u, i);
                 const int e = s_uniq_e[u] - p.expert_base;
                 const unsigned bytes = (unsigned)((size_t)count * rowH * sizeof(T));
                 const int n = nA + k;
@@ -364,8 +352,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
                 if (cta == 0 && k == nB - 1) trace_stamp(p.ctl, 16);
                 if (dst) {
                     const size_t off = ((size_t)e * p.I + i) * rowH;
-                    bulk_copy_g2s(dst, static_cast<const T*>(p.egate) + off, bytes, &full_bar[n % NS]);
-                    bulk_copy_g2s(dst + up_off * sizeof(T), static_cast<const T*>(p.eup) + off, bytes, &full_bar[n % NS]);
+                    bulk_copy_g2s(dst, static_cast<const T*>(p.egate) + off, bytes, &full_bar[stage_of(n)]);
+                    bulk_copy_g2s(dst + up_off * sizeof(T), static_cast<const T*>(p.eup) + off, bytes, &full_bar[stage_of(n)]);
                 }
             }
             const unsigned cbytes = (unsigned)((size_t)hr * p.I * sizeof(T));
@@ -379,7 +367,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
                     for (int u = ua; u < ub; ++u) {
                         const int e = s_uniq_e[u] - p.expert_base;
                         bulk_copy_g2s(dst + (size_t)(u - ua) * p.hr_max * p.I * sizeof(T),
-                                      static_cast<const T*>(p.edown) + ((size_t)e * p.H + h0) * p.I, cbytes, &full_bar[n % NS]);
+                                      static_cast<const T*>(p.edown) + ((size_t)e * p.H + h0) * p.I, cbytes, &full_bar[stage_of(n)]);
                     }
                 }
             }
@@ -395,6 +383,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     // =====================================================================================
     const int group = warp / kRingGroupWarps;
     const int wi = warp % kRingGroupWarps;
+    const int gtid = tid - group * kRingGroupThreads;  // thread index inside the group
+    const int fg = lane >> 2, ft = lane & 3;           // MMA fragment coordinates of this lane
+    float* gred = red + (size_t)group * 2 * kRingGroupWarps * 128;
+    int gbuf = 0;
 
     // ---- phase 0: RMSNorm of the tokens into shared memory (as T) ----
     // x and the norm weight are fetched together so that the phase costs one memory round trip.
@@ -444,27 +436,69 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
         named_barrier(1, kRingConsumerThreads);
     }
-    float xr[kRingXChunks][8];
-    if (XR) {
-#pragma unroll
-        for (int j = 0; j < kRingXChunks; ++j) {
-            const int c = lane + 32 * j;
-            if (c < Hc) {
-                unpack_u4<T>(lds128(xs + 8 * c), xr[j]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) xr[j][i] = 0.0f;
-            }
-        }
-    }
     if (tracer) trace_stamp(p.ctl, 1);
 
-    const unsigned long long all_tokens = (p.ntok >= 64) ? ~0ull : ((1ull << p.ntok) - 1ull);
-
     bool ok = true;
+
+    // One stage of rows of length hidden against all tokens.  The four warps of the group split the
+    // contraction, leave their 16 x 8 partial tiles in shared memory, meet at the group's barrier and
+    // then every thread of the group owns one (row, column) of the summed tile.  kind: 0 router rows,
+    // 1 shared (gate, up) pairs, 2 routed (gate, up) pairs of the expert with pair mask `mask`.
+    // A warp whose wait ran out still walks through the barrier so that its group never hangs.
+    auto consume_rows = [&](int n, int kind, int first, int count, unsigned long long mask, int i0) {
+        const int stage = stage_of(n);
+        bool got = ok;
+        if (got) got = mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
+        if (!got) ok = false;
+        float* mine = gred + ((size_t)gbuf * kRingGroupWarps + wi) * 128;
+        if (got) {
+            const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
+            const int nrows = (kind == 0) ? count : (PR + count);
+            float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            tile_times_vectors<T>(d, sbase, p.H, nrows, xs, p.H, p.ntok, p.H, wi, kRingGroupWarps, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // the stage has been read
+            *reinterpret_cast<float2*>(mine + fg * 8 + 2 * ft) = make_float2(d[0], d[1]);
+            *reinterpret_cast<float2*>(mine + (fg + 8) * 8 + 2 * ft) = make_float2(d[2], d[3]);
+        }
+        named_barrier(2 + group, kRingGroupThreads);
+        if (got) {
+            const float* all = gred + (size_t)gbuf * kRingGroupWarps * 128;
+            const int r = gtid >> 3, c = gtid & 7;
+            if (r < count) {
+                if (kind == 0) {
+                    if (c < p.ntok) {
+                        float v = 0.0f;
+#pragma unroll
+                        for (int w = 0; w < kRingGroupWarps; ++w) v += all[w * 128 + r * 8 + c];
+                        p.logits[(size_t)c * p.E + first + r] = v;
+                    }
+                } else {
+                    int tok = -1, slot = 0;
+                    if (kind == 1) {
+                        if (c < p.ntok) { tok = c; slot = c; }
+                    } else if (c < __popcll(mask)) {
+                        slot = nth_set_bit(mask, c);
+                        tok = fdiv(slot, p.fd_K);
+                    }
+                    if (tok >= 0) {
+                        float gsum = 0.0f, usum = 0.0f;
+#pragma unroll
+                        for (int w = 0; w < kRingGroupWarps; ++w) {
+                            gsum += all[w * 128 + r * 8 + tok];
+                            usum += all[w * 128 + (PR + r) * 8 + tok];
+                        }
+                        const float a = silu(gsum) * usum;
+                        if (kind == 1) p.sact[(size_t)slot * p.Is + first + r] = a;
+                        else p.act[(size_t)slot * p.I + i0 + r] = a;
+                    }
+                }
+            }
+        }
+        gbuf ^= 1;
+    };
+
     // ---- phase A: router rows, then shared gate+up rows ----
-    // (A warp that has given up keeps walking the loops without touching data, so that every
-    // named barrier below is still reached by all consumer warps.)
     unsigned bar_target = 0;
     for (int n = 0; n <= nA; ++n) {
         if (n == nA1) {
@@ -474,58 +508,15 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
         if (n == nA) break;
         if (n % kRingGroups != group) continue;
-        const int stage = n % NS;
-        if (ok) ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
-        if (!ok) continue;
-        if (tracer && n == 0) trace_stamp(p.ctl, 10);
-        const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
         int first, count;
         if (n < nA1) {
-            chunk_span(r0, r1, p.rows_h, n, first, count);
-            for (int j = wi; j < count; j += 2 * kRingGroupWarps) {
-                const bool two = (j + kRingGroupWarps) < count;
-                const T* row0 = sbase + (size_t)j * rowH;
-                const T* row1 = sbase + (size_t)(j + kRingGroupWarps) * rowH;
-                if (XR) {
-                    float v0, v1;
-                    row_dot_regs2<T>(row0, row1, two, Hc, lane, xr, v0, v1);
-                    if (lane == 0) {
-                        p.logits[first + j] = v0;
-                        if (two) p.logits[first + j + kRingGroupWarps] = v1;
-                    }
-                } else {
-                    int tok[kRingMaxTokens];
-#pragma unroll
-                    for (int t = 0; t < kRingMaxTokens; ++t) tok[t] = (t < p.ntok) ? t : 0;
-                    float v0[kRingMaxTokens], v1[kRingMaxTokens];
-                    row_dot_smem2<T, kRingMaxTokens>(row0, row1, two, Hc, lane, xs, tok, p.H, v0, v1);
-                    if (lane == 0) {
-#pragma unroll
-                        for (int t = 0; t < kRingMaxTokens; ++t) {
-                            if (t < p.ntok) {
-                                p.logits[(size_t)t * p.E + first + j] = v0[t];
-                                if (two) p.logits[(size_t)t * p.E + first + j + kRingGroupWarps] = v1[t];
-                            }
-                        }
-                    }
-                }
-            }
+            chunk_span(r0, r1, p.rows_h, mA1, n, first, count);
+            consume_rows(n, 0, first, count, 0ull, 0);
         } else {
-            chunk_span(s0, s1, PR, n - nA1, first, count);
-            for (int j = wi; j < count; j += kRingGroupWarps) {
-                const T* grow = sbase + (size_t)j * rowH;
-                const T* urow = sbase + up_off + (size_t)j * rowH;
-                if (XR) {
-                    float g, u;
-                    row_dot_regs2<T>(grow, urow, true, Hc, lane, xr, g, u);
-                    if (lane == 0) p.sact[first + j] = silu(g) * u;
-                } else {
-                    pair_rows_dispatch<T>(grow, urow, Hc, p.H, lane, xs, all_tokens, 0, p.sact, p.Is, first + j);
-                }
-            }
+            chunk_span(s0, s1, PR, mA2, n - nA1, first, count);
+            consume_rows(n, 1, first, count, 0ull, 0);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (tracer && n == 0) trace_stamp(p.ctl, 10);
     }
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
 
@@ -662,34 +653,18 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     if (tracer) trace_stamp(p.ctl, 5);
 
     // ---- phase B: routed gate+up rows -> silu(g) * u per (pair, channel) ----
-    const long long tasks = (long long)p.I * n_unique;
-    const int t0 = (int)(tasks * cta / ncta), t1 = (int)(tasks * (cta + 1) / ncta);
-    const int nB = chunks_in(t0, t1, PR);
-    for (int k = 0; k < nB && ok; ++k) {
+    const int tasks = p.I * n_unique;
+    const int t0 = fdiv(tasks * cta, p.fd_ncta), t1 = fdiv(tasks * (cta + 1), p.fd_ncta);
+    const int nB = chunks_in(t0, t1, p.fd_pr);
+    const int mB = fdiv(t0, p.fd_pr);
+    for (int k = 0; k < nB; ++k) {
         const int n = nA + k;
         if (n % kRingGroups != group) continue;
-        const int stage = n % NS;
-        ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
-        if (!ok) break;  // no named barrier inside this loop, leaving early is safe
+        int first, count, u, i0;
+        chunk_span(t0, t1, PR, mB, k, first, count);
+        fdivmod(first, p.fd_I, u, i0);
+        consume_rows(n, 2, first, count, s_uniq_m[u], i0);
         if (tracer && k < kRingGroups) trace_stamp(p.ctl, 11);
-        const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
-        int first, count;
-        chunk_span(t0, t1, PR, k, first, count);
-        const int u = first / p.I, i0 = first - u * p.I;
-        const unsigned long long m = s_uniq_m[u];
-        for (int j = wi; j < count; j += kRingGroupWarps) {
-            const T* grow = sbase + (size_t)j * rowH;
-            const T* urow = sbase + up_off + (size_t)j * rowH;
-            if (XR) {
-                float g, up;
-                row_dot_regs2<T>(grow, urow, true, Hc, lane, xr, g, up);
-                if (lane == 0) p.act[(size_t)(__ffsll((long long)m) - 1) * p.I + i0 + j] = silu(g) * up;
-            } else {
-                pair_rows_dispatch<T>(grow, urow, Hc, p.H, lane, xs, m, p.K, p.act, p.I, i0 + j);
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
 
@@ -712,12 +687,13 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     if (tid == 0) cta_stamp(p.ctl, cta, 1);
     ok = (s_flag != 0);
 
-    // ---- activations into shared memory (the token region is reused), split layout ----
-    const int Ic = p.I >> 3, Isc = p.Is >> 3;
-    const int a_half = Ic * 4, a_stride = Ic * 8;
-    const int sa_half = Isc * 4, sa_stride = Isc * 8;
+    // ---- activations into shared memory (the token region is reused) as a high and a low half in
+    //      the storage dtype: act = hi + lo to ~2^-17 relative, and both halves are MMA operands ----
     const int npairs = p.ntok * p.K;
-    float* sacts = acts + (size_t)npairs * a_stride;
+    const size_t act_elems = (size_t)npairs * p.I + (size_t)p.ntok * p.Is;
+    T* acts_lo = acts_hi + act_elems;
+    const size_t shared_base = (size_t)npairs * p.I;  // element offset of the shared expert's activations
+    const int nC_all = (hr > 0) ? fdiv(n_unique + p.epc - 1, p.fd_epc) : 0;
     if (ok) {
         // one item = four consecutive channels of one (pair | shared token) = one 16-byte load; a
         // thread issues kActBatch loads before it touches the results
@@ -726,86 +702,105 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         const int items = routed_items + p.ntok * q_is;
         for (int base = 0; base < items; base += kRingConsumerThreads * kActBatch) {
             float4 v[kActBatch];
-            int dst[kActBatch];
+            long long dst[kActBatch];
 #pragma unroll
             for (int q = 0; q < kActBatch; ++q) {
                 const int it = base + q * kRingConsumerThreads + tid;
                 dst[q] = -1;
                 v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (it < routed_items) {
-                    const int pair = it / q_i, i = (it - pair * q_i) * 4;
+                    int pair, i;
+                    fdivmod(it, p.fd_qi, pair, i);
+                    i *= 4;
                     const int e = s_pair_e[pair];
                     if (e >= p.expert_base && e < p.expert_base + p.local_experts) {
                         v[q] = __ldcg(reinterpret_cast<const float4*>(p.act + (size_t)pair * p.I + i));
-                        dst[q] = pair * a_stride + split_index(i, a_half);
+                        dst[q] = (long long)pair * p.I + i;
                     }
                 } else if (it < items) {
                     const int r = it - routed_items;
-                    const int b = r / q_is, i = (r - b * q_is) * 4;
+                    int b, i;
+                    fdivmod(r, p.fd_qis, b, i);
+                    i *= 4;
                     v[q] = __ldcg(reinterpret_cast<const float4*>(p.sact + (size_t)b * p.Is + i));
-                    dst[q] = npairs * a_stride + b * sa_stride + split_index(i, sa_half);
+                    dst[q] = (long long)shared_base + (long long)b * p.Is + i;
                 }
             }
 #pragma unroll
-            for (int q = 0; q < kActBatch; ++q)
-                if (dst[q] >= 0) *reinterpret_cast<float4*>(acts + dst[q]) = v[q];
+            for (int q = 0; q < kActBatch; ++q) {
+                if (dst[q] >= 0) {
+                    const float in[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+                    T hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        hi[i] = from_float<T>(in[i]);
+                        lo[i] = from_float<T>(in[i] - to_float<T>(hi[i]));
+                    }
+                    *reinterpret_cast<uint2*>(acts_hi + dst[q]) = *reinterpret_cast<const uint2*>(hi);
+                    *reinterpret_cast<uint2*>(acts_lo + dst[q]) = *reinterpret_cast<const uint2*>(lo);
+                }
+            }
         }
     }
     named_barrier(1, kRingConsumerThreads);
     if (tracer) trace_stamp(p.ctl, 8);
 
-    // ---- phase C: down rows.  part[slot][row]: slot < npairs routed pairs, then one per token (shared) ----
-    const int nC = (hr > 0) ? (n_unique + p.epc - 1) / p.epc : 0;
-    if (ok && hr > 0 && p.Is > 0) {
-        ok = mbar_wait(sdown_bar, 0, &s_abort);
-        if (ok) {
-            // shared expert: row j -> warp j % 12; a warp does its (up to two) rows together
-            for (int j = warp; j < hr; j += 2 * kRingConsumerWarps) {
-                const int nrows = (j + kRingConsumerWarps < hr) ? 2 : 1;
-                for (int t = 0; t < p.ntok; ++t) {
-                    float v[2];
-                    rows_dot_act<T, 2>(sdown_buf + (size_t)j * p.Is, kRingConsumerWarps * p.Is, nrows, sacts + t * sa_stride, sa_half,
-                                       Isc, lane, v);
-                    if (lane == 0) {
-                        part[(npairs + t) * p.hr_max + j] = v[0];
-                        if (nrows == 2) part[(npairs + t) * p.hr_max + j + kRingConsumerWarps] = v[1];
-                    }
-                }
+    // ---- phase C: down rows.  part[slot][row]: slot < npairs routed pairs, then one per token (shared).
+    //      One warp contracts one expert's block of rows over the whole intermediate length. ----
+    const int nC = nC_all;
+    if (warp == kRingConsumerWarps - 1 && hr > 0 && p.Is > 0) {
+        // shared expert: rows from the dedicated buffer, columns = tokens
+        bool got = ok;
+        if (got) got = mbar_wait(sdown_bar, 0, &s_abort);
+        if (!got) ok = false;
+        if (got) {
+            float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const T* ch = (fg < p.ntok) ? acts_hi + shared_base + (size_t)fg * p.Is : nullptr;
+            const T* cl = (fg < p.ntok) ? acts_lo + shared_base + (size_t)fg * p.Is : nullptr;
+            tile_times_split_vectors<T>(d, sdown_buf, p.Is, hr, ch, cl, p.Is, lane);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int row = fg + ((q & 2) ? 8 : 0), col = 2 * ft + (q & 1);
+                if (row < hr && col < p.ntok) part[(npairs + col) * p.hr_max + row] = d[q];
             }
         }
     }
     if (tracer) trace_stamp(p.ctl, 12);
-    for (int k = 0; k < nC && ok; ++k) {
+    for (int k = 0; k < nC; ++k) {
         const int n = nA + nB + k;
         if (n % kRingGroups != group) continue;
-        const int stage = n % NS;
-        ok = mbar_wait(&full_bar[stage], (n / NS) & 1, &s_abort);
-        if (!ok) break;
+        const int stage = stage_of(n);
+        bool got = ok;
+        if (got) got = mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
+        if (!got) { ok = false; continue; }
         if (tracer && k < kRingGroups) trace_stamp(p.ctl, 13);
         if (tracer && k >= kRingGroups) trace_stamp(p.ctl, 19);
-        const int ua = k * p.epc, ub = min(n_unique, ua + p.epc);
-        for (int u = ua; u < ub; ++u) {
-            const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)(u - ua) * p.hr_max * p.I;
+        const int u = k * p.epc + wi;
+        if (wi < p.epc && u < n_unique) {
+            const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)wi * p.hr_max * p.I;
             const unsigned long long mask = s_uniq_m[u];
-            // rows wi + 4q of this expert's block belong to this warp; four of them are done together
-            for (int j = wi; j < hr; j += 4 * kRingGroupWarps) {
-                const int nrows = min(4, (hr - j + kRingGroupWarps - 1) / kRingGroupWarps);
-                unsigned long long m = mask;
-                while (m) {
-                    const int pair = __ffsll((long long)m) - 1;
-                    m &= m - 1;
-                    float v[4];
-                    rows_dot_act<T, 4>(sbase + (size_t)j * p.I, kRingGroupWarps * p.I, nrows, acts + pair * a_stride, a_half, Ic, lane, v);
-                    if (lane == 0) {
+            const int ncol = __popcll(mask);
+            const T* ch = nullptr;
+            const T* cl = nullptr;
+            if (fg < ncol) {
+                const int pair = nth_set_bit(mask, fg);
+                ch = acts_hi + (size_t)pair * p.I;
+                cl = acts_lo + (size_t)pair * p.I;
+            }
+            float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (tracer && k < kRingGroups) trace_stamp(p.ctl, 20);
+            tile_times_split_vectors<T>(d, sbase, p.I, hr, ch, cl, p.I, lane);
+            if (tracer && k < kRingGroups) trace_stamp(p.ctl, 21);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            if (q < nrows) part[pair * p.hr_max + j + q * kRingGroupWarps] = v[q];
-                    }
-                }
+            for (int q = 0; q < 4; ++q) {
+                const int row = fg + ((q & 2) ? 8 : 0), col = 2 * ft + (q & 1);
+                if (row < hr && col < ncol) part[nth_set_bit(mask, col) * p.hr_max + row] = d[q];
             }
         }
         __syncwarp();
+        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 22);
         if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 23);
     }
     if (tracer) trace_stamp(p.ctl, 14);
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
@@ -815,8 +810,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     // ---- combine in slot order, add the residual, round once ----
     T* out = static_cast<T*>(p.out);
-    for (int idx = tid; idx < p.ntok * hr; idx += kRingConsumerThreads) {
-        const int b = idx / hr, j = idx - b * hr;
+    for (int idx = tid; idx < p.ntok * kRingTileRows; idx += kRingConsumerThreads) {
+        const int b = idx >> 4, j = idx & (kRingTileRows - 1);
+        if (j >= hr) continue;
         float v = 0.0f;
         for (int k = 0; k < p.K; ++k) {
             const int pair = b * p.K + k;
@@ -838,14 +834,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 // -------------------------------------------------------------------------------------------
 // Host side
 // -------------------------------------------------------------------------------------------
-namespace {
-
-template <typename T>
-const void* ring_kernel_for(bool xr) {
-    return xr ? (const void*)moe_decode_ring_kernel<T, true> : (const void*)moe_decode_ring_kernel<T, false>;
-}
-
-}  // namespace
 
 // Launches the streaming variant when the shapes suit it and sets *handled; otherwise leaves
 // *handled false (no error) so that the caller uses the general kernel.
@@ -853,9 +841,9 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
     *handled = false;
     if (a->dtype != MK36_BF16 && a->dtype != MK36_F16) return MK36_OK;
     const int H = a->hidden, E = a->experts, K = a->top_k, I = a->intermediate, Is = a->shared_intermediate;
-    if (K <= 0 || I <= 0 || H % 8 != 0 || I % 8 != 0 || Is % 8 != 0) return MK36_OK;
-    const int row_h = H * 2;
-    int rows_h = kRingStageBytes / row_h;
+    if (K <= 0 || I <= 0 || H % 32 != 0 || I % 32 != 0 || Is % 32 != 0) return MK36_OK;
+    int rows_h = kRingStageBytes / (H * 2);
+    if (rows_h > kRingTileRows) rows_h = kRingTileRows;
     rows_h &= ~1;
     if (rows_h < 2) return MK36_OK;
     const int pr = rows_h / 2;
@@ -868,9 +856,13 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
     if (!dev) return MK36_ERR_LAUNCH;
     const int ncta = dev->sm_count;
     const int hr_max = (H + ncta - 1) / ncta;
+    if (hr_max > kRingTileRows) return MK36_OK;
     const size_t down_block = (size_t)hr_max * I * 2;  // one expert's output rows of this CTA
     if (down_block > (size_t)kRingStageBytes || (size_t)hr_max * Is * 2 > 32768) return MK36_OK;
-    const int epc = (int)(kRingStageBytes / down_block);
+    if ((long long)I * kRingMaxPairs * ncta >= (1ll << 31) || (long long)H * ncta >= (1ll << 31) || (long long)E * ncta >= (1ll << 31))
+        return MK36_OK;  // the kernel's index arithmetic is 31-bit
+    int epc = (int)(kRingStageBytes / down_block);
+    if (epc > kRingGroupWarps) epc = kRingGroupWarps;
 
     int tb = kRingMaxTokens;
     while (tb > 1 && (long long)tb * K > kRingMaxPairs) tb >>= 1;
@@ -894,9 +886,10 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
         const int pairs = tb * K;
         p.off_sdown = take((size_t)hr_max * Is * 2, 128);
         const size_t xs_bytes = (size_t)tb * H * 2;
-        const size_t act_bytes = ((size_t)pairs * I + (size_t)tb * Is) * 4;
+        const size_t act_bytes = ((size_t)pairs * I + (size_t)tb * Is) * 4;  // high + low halves
         p.off_act = take(xs_bytes > act_bytes ? xs_bytes : act_bytes, 128);
         p.off_part = take((size_t)(pairs + tb) * hr_max * 4, 16);
+        p.off_red = take((size_t)kRingGroups * 2 * kRingGroupWarps * 128 * 4, 16);
         p.off_logits = take(E > 32 * kTopkPerLane ? (size_t)tb * E * 4 : 16, 16);
         p.off_uniq_e = take(kRingMaxPairs * 4, 16);
         p.off_uniq_m = take(kRingMaxPairs * 8, 16);
@@ -906,8 +899,9 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
         p.off_ring = take(0, 128);
         const long long room = (long long)dev->max_smem_optin - (long long)off - 1024;
         nstages = (int)(room / kRingStageBytes);
-        if (nstages > kRingMaxStages) nstages = kRingMaxStages;
-        if (nstages >= 3) break;
+        // every consumer group owns one or two stages of its own (see stage_of below)
+        nstages = (nstages >= 2 * kRingGroups) ? 2 * kRingGroups : (nstages >= kRingGroups ? kRingGroups : 0);
+        if (nstages > 0) break;
     }
     if (tb < 1) return MK36_OK;
     const size_t smem_bytes = (size_t)p.off_ring + (size_t)nstages * kRingStageBytes;
@@ -943,15 +937,22 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
     p.rows_h = rows_h;
     p.epc = epc;
     p.hr_max = hr_max;
-    p.l2_prefetch = options().l2_prefetch;
+    p.log2_depth = (nstages >= 2 * kRingGroups) ? 1 : 0;
+    p.fd_ncta = make_fastdiv(ncta);
+    p.fd_rows_h = make_fastdiv(rows_h);
+    p.fd_pr = make_fastdiv(pr);
+    p.fd_I = make_fastdiv(I);
+    p.fd_K = make_fastdiv(K);
+    p.fd_qi = make_fastdiv(I / 4);
+    p.fd_qis = make_fastdiv(Is > 0 ? Is / 4 : 1);
+    p.fd_epc = make_fastdiv(epc);
 
+    const void* kernel = (a->dtype == MK36_BF16) ? (const void*)moe_decode_ring_kernel<__nv_bfloat16>
+                                                 : (const void*)moe_decode_ring_kernel<__half>;
+    MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     const size_t es = 2;
     for (int b0 = 0; b0 < a->batch; b0 += tb) {
-        const int ntok = (a->batch - b0 < tb) ? (a->batch - b0) : tb;
-        const bool xr = (ntok == 1 && H <= kRingXChunks * 32 * 8);
-        const void* kernel = (a->dtype == MK36_BF16) ? ring_kernel_for<__nv_bfloat16>(xr) : ring_kernel_for<__half>(xr);
-        MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-        p.ntok = ntok;
+        p.ntok = (a->batch - b0 < tb) ? (a->batch - b0) : tb;
         p.x = static_cast<const unsigned char*>(a->x) + (size_t)b0 * H * es;
         p.out = a->out ? static_cast<unsigned char*>(a->out) + (size_t)b0 * H * es : nullptr;
         p.partial_out = a->partial_out ? a->partial_out + (size_t)b0 * H : nullptr;
