@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "moe_decode_ring.cu",
     "dense_ffn_decode.cu",
     "attention_decode.cu",
+    "attention_decode_mma.cu",
     "linear_attention_decode.cu",
 ]
 LIB_NAME = "libmk36.so"

@@ -12,7 +12,7 @@
 // the whole cache, fp32 accumulation, one rounding to the output dtype.
 #include <cfloat>
 
-#include "mk36_common.cuh"
+#include "mk36_attention.cuh"
 
 namespace mk36 {
 
@@ -20,22 +20,6 @@ constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
 constexpr int kMaxHeadDim = 256;
 constexpr int kDimPerLane = kMaxHeadDim / 32;
-
-struct AttnParams {
-    const void* q;
-    const void* k;
-    const void* v;
-    void* out;
-    Control* ctl;
-    float* part_o;  // [B][Hq][splits][D]
-    float* part_m;  // [B][Hq][splits]
-    float* part_l;  // [B][Hq][splits]
-    int B, Hq, Hkv, D, T;
-    int group;      // Hq / Hkv
-    int subgroups;  // ceil(group / GP)
-    int splits;
-    float scale;
-};
 
 // Generic path: any dtype, any head_dim <= 256, CUDA cores.  Lane l owns channels l, l+32, ...
 template <typename T, int GP>
@@ -146,32 +130,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_decode_generic_kernel(
     }
 
     // ---- one grid barrier, then every CTA merges a share of the outputs ----
-    if (!grid_barrier(p.ctl, gridDim.x, 0, kStatusAttnBarrier, &s_flag)) return;
-    if (threadIdx.x == 0) barrier_finish(p.ctl, gridDim.x);
-
-    const int dchunks = (p.D + 31) / 32;
-    const int items = p.B * p.Hq * dchunks;
-    const int total_warps = gridDim.x * kAttnWarps;
-    T* out = static_cast<T*>(p.out);
-    for (int it = blockIdx.x * kAttnWarps + warp; it < items; it += total_warps) {
-        const int dc = it % dchunks;
-        const int bh = it / dchunks;
-        const int d = dc * 32 + lane;
-        const float* pm = p.part_m + (size_t)bh * p.splits;
-        const float* pl = p.part_l + (size_t)bh * p.splits;
-        const float* po = p.part_o + (size_t)bh * p.splits * p.D;
-        float mm = -INFINITY;
-        for (int s = lane; s < p.splits; s += 32) mm = fmaxf(mm, __ldcg(pm + s));
-        mm = warp_max(mm);
-        float acc = 0.0f, lsum = 0.0f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float ms = __ldcg(pm + s);
-            const float sc = (ms == -INFINITY) ? 0.0f : expf(ms - mm);
-            lsum = fmaf(sc, __ldcg(pl + s), lsum);
-            if (d < p.D) acc = fmaf(sc, __ldcg(po + (size_t)s * p.D + d), acc);
-        }
-        if (d < p.D) out[(size_t)bh * p.D + d] = from_float<T>(acc / lsum);
-    }
+    attention_merge_partials<T>(p, kAttnWarps, &s_flag);
 }
 
 // -------------------------------------------------------------------------------------------
@@ -232,9 +191,16 @@ void plan_generic(const mk36_attention_args& a, int max_ctas, AttnPlan* plan) {
 
 }  // namespace
 
+int attention_decode_mma_launch(const mk36_attention_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled);
+
 int attention_decode_launch(const mk36_attention_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int rc = check_attention_args(a);
     if (rc != MK36_OK) return rc;
+    if (!options().force_generic) {
+        bool handled = false;
+        rc = attention_decode_mma_launch(a, workspace, workspace_bytes, stream, &handled);
+        if (rc != MK36_OK || handled) return rc;
+    }
     const DeviceInfo* dev = current_device_info();
     if (!dev) return MK36_ERR_LAUNCH;
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)

@@ -74,6 +74,22 @@ def test_moe_general_kernel_matches_oracle(name, cuda_device):
     assert lib.mk36_set_option(b"no_such_option", 1) == cabi.MK36_ERR_INVALID_ARG
 
 
+@pytest.mark.parametrize("name", ["attn_27b_bf16_t1000", "attn_35b_bf16_t4096", "attn_35b_bf16_b2_t2500"])
+def test_attention_general_kernel_matches_oracle(name, cuda_device):
+    """Shapes that normally take the tensor-core attention kernel, forced through the general one."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    cabi.check(lib.mk36_set_option(b"force_generic", 1))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(b"force_generic", 0))
+    assert_output_parity(got["out"], run_oracle(case, spec)["out"], what=name + " (general kernel)")
+
+
 @pytest.mark.parametrize("case", LINEAR, ids=lambda c: c.name)
 def test_linear_attention_state_drift(case, cuda_device):
     """64 consecutive steps, feeding the new state back: state error after every step, outputs at
