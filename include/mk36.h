@@ -223,6 +223,24 @@ MK36_API size_t mk36_attention_workspace_bytes(const mk36_attention_args* args);
 MK36_API int mk36_full_attention_decode(const mk36_attention_args* args, void* workspace,
                                         size_t workspace_bytes, void* stream);
 
+/* Full-attention decode for callers that cannot provide a workspace.  This entry point has no
+ * counterpart in the reference: it exists for hosts that bind the library over a plain C boundary
+ * and own no device allocator, or that sit in a request loop where cudaMalloc / cudaFree (which
+ * synchronise the device) must not be called.  Same arithmetic, same kernels and same results as
+ * mk36_full_attention_decode; the split partials and the barrier control block live in a fixed
+ * MK36_STATIC_SCRATCH_BYTES device array inside the library, and the call performs no device
+ * allocation of any kind.
+ *   - A problem whose launch plan needs more scratch than the array holds fails with
+ *     MK36_ERR_WORKSPACE and a message that names the limit (on a 148-SM part every supported
+ *     shape, head_dim <= 256, needs less than 1.3 MB).
+ *   - All calls on one GPU share the array.  Each call clears the control block on `stream` before
+ *     its kernels; calls that may overlap on the same GPU (other streams or host threads) race on
+ *     the array and their results are undefined - serialise them.
+ *   - The first call on each GPU also looks up the array's device address; make that first call
+ *     outside of any stream capture. */
+#define MK36_STATIC_SCRATCH_BYTES (2u << 20)
+MK36_API int mk36_full_attention_decode_static(const mk36_attention_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Linear-attention recurrent decode step with an fp32 state:
  *     S'[b,h] = decay * S[b,h] + k[b,hk] (x) (beta * v[b,h]);   out[b,h] = q[b,hk]^T S'[b,h]

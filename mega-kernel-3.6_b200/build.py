@@ -34,6 +34,7 @@ CUDA_SOURCES = [
     "dense_ffn_decode.cu",
     "attention_decode.cu",
     "attention_decode_mma.cu",
+    "attention_decode_static.cu",
     "linear_attention_decode.cu",
 ]
 LIB_NAME = "libmk36.so"

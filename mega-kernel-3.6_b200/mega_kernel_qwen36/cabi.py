@@ -78,6 +78,7 @@ SIGNATURES = {
     "mk36_dense_ffn_decode": (C.c_int, [C.POINTER(DenseFfnArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_attention_workspace_bytes": (C.c_size_t, [C.POINTER(AttentionArgs)]),
     "mk36_full_attention_decode": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mk36_full_attention_decode_static": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
     "mk36_linear_attention_decode": (C.c_int, [C.POINTER(LinearAttentionArgs), C.c_void_p]),
 }
 
