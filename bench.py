@@ -315,7 +315,7 @@ def workload_config(batch, gpus, n_sets):
         "workload": f"Qwen3.6-35B-A3B-shape MoE decode layer, batch {batch}: hidden 2048, 256 experts, top-8, expert "
                     "intermediate 512, shared expert 512, RMSNorm eps 1e-6, residual",
         "batch": batch,
-        "parallelism": "single GPU" if gpus == 1 else f"expert parallel x{gpus} (256/{gpus} experts + 1/{gpus} of the shared expert per GPU, one fp32 all-reduce)",
+        "parallelism": "single GPU" if gpus == 1 else f"expert parallel x{gpus} (256/{gpus} experts + 1/{gpus} of the shared expert per GPU, fp32 partial outputs summed across GPUs)",
     }
     if n_sets:
         cfg["l2"] = f"inputs larger than L2: steps rotate over {n_sets} full weight sets (the step's own bytes x sets > 126 MB) and 16 tokens"
@@ -332,6 +332,8 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="full weight sets to rotate over")
     ap.add_argument("--no-others", action="store_true", help="skip the context measurements of the other ops")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: sum the ranks' partials inside the kernel over peer memory, or with an NCCL all-reduce")
     ns = ap.parse_args()
     ns.warmup = max(ns.warmup, 3)
 
@@ -418,25 +420,51 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
     n_tokens = 16
     xs = [syn.hidden_states(ns.batch, syn.MOE_35B_A3B.hidden, seed=100 + i).to(device) for i in range(n_tokens)]
 
+    # a local (non-collective) launch first: module loading on one rank must not eat into the
+    # bounded waits of the others
+    w0 = shards[0].weights
+    mk.ops._C.moe_decode_partial(xs[0], *[getattr(w0, f) for f in syn.MOE_WEIGHT_FIELDS], 1e-6, 8, shards[0].expert_base)
+    torch.cuda.synchronize()
+    exchange = None if ns.collective == "nccl" else parallel.PeerExchange(device)
+    dist.barrier()
+
     def step(i):
-        return parallel.moe_decode_ep(xs[i % n_tokens], shards[i % len(shards)], top_k=8)
+        return parallel.moe_decode_ep(xs[i % n_tokens], shards[i % len(shards)], top_k=8, exchange=exchange)
 
     sampler = ClockSampler(device.index)
     if rank == 0:
         sampler.start()
-    for i in range(ns.warmup):
-        step(i)
-    torch.cuda.synchronize()
+    if exchange is not None:
+        # one launch per step and nothing else: K steps in one CUDA graph, as on a single GPU; the ranks
+        # meet inside every step, so the replays stay in lock-step
+        fns = [(lambda i=i: step(i)) for i in range(ns.steps)]
+        dist.barrier()
+        ms_local, graph, stream = time_graph(fns, ns.warmup)
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            graph.replay()
+            end.record(stream)
+            end.synchronize()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        timing = "CUDA graph of all steps (one kernel per step per GPU, cross-GPU sum inside the kernel), CUDA events, max over ranks"
+    else:
+        for i in range(ns.warmup):
+            step(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(ns.steps):
+            step(i)
+        end.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        timing = "eager launches (kernel + NCCL all-reduce + residual per step), CUDA events, max over ranks"
     dist.barrier()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(ns.steps):
-        step(i)
-    end.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = torch.tensor([start.elapsed_time(end)], device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     e2e = None
     host_x = [x.cpu().pin_memory() for x in xs]
@@ -447,7 +475,7 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
     t0 = time.perf_counter()
     for i in range(ns.steps):
         x_dev.copy_(host_x[i % n_tokens], non_blocking=True)
-        out, _, _ = parallel.moe_decode_ep(x_dev, shards[i % len(shards)], top_k=8)
+        out, _, _ = parallel.moe_decode_ep(x_dev, shards[i % len(shards)], top_k=8, exchange=exchange)
         host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     torch.cuda.synchronize()
@@ -468,9 +496,13 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
                          "frac": round(gbs / (peak * world), 4), "peak_kind": f"of {peak_kind} x {world} GPUs",
                          "algorithmic_bytes_per_launch": nbytes_alg, "traffic": None},
             "cpu_baseline": None, "e2e": e2e, "gpu_launches": ns.steps, "clocks": clocks,
-            "timing": "eager launches (kernel + NCCL all-reduce + residual per step), CUDA events, max over ranks",
+            "timing": timing,
         }
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if exchange is not None:
+        exchange.close()
     dist.destroy_process_group()
 
 

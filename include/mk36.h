@@ -276,6 +276,45 @@ typedef struct mk36_linear_attention_args {
 
 MK36_API int mk36_linear_attention_decode(const mk36_linear_attention_args* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Multi-GPU (one process per GPU, all GPUs on one NVLink / NVSwitch box).
+ *
+ * The reference is single-GPU; these entry points have no counterpart there.  They run the same
+ * kernels as mk36_moe_decode / mk36_dense_ffn_decode on the rank's shard of the weights
+ * (expert-parallel MoE: experts [expert_base, expert_base + local_experts) plus this rank's slice
+ * of the shared expert's intermediate rows; tensor-parallel dense FFN: this rank's gate/up rows and
+ * down columns) and finish, inside the same launch, with the sum of all ranks' fp32 partial outputs
+ * over peer memory, the residual and the rounding.  Every rank ends with the same, bit-identical,
+ * full `out`; `partial_out` must be NULL.
+ *
+ * Each rank owns one exchange buffer of mk36_comm_buffer_bytes() bytes from mk36_comm_buffer_alloc
+ * (a plain cudaMalloc, zero-filled: CUDA IPC can export nothing smaller than a whole allocation;
+ * this is the only device memory the library allocates, once at set-up).  The ranks swap
+ * mk36_ipc_export handles by any host channel, map the others' buffers with mk36_ipc_open, and
+ * describe the result in mk36_comm (buffers[rank] is the rank's own pointer).  All ranks must make
+ * the same sequence of *_ep / *_tp calls with the same shapes.  A device-side wait for a peer is
+ * bounded (about a second); when it runs out the status word of the workspace is set to 401 and
+ * the kernel ends. */
+#define MK36_MAX_RANKS 8
+#define MK36_IPC_HANDLE_BYTES 64
+
+typedef struct mk36_comm {
+    int32_t rank;
+    int32_t world;
+    void* buffers[MK36_MAX_RANKS];
+} mk36_comm;
+
+MK36_API size_t mk36_comm_buffer_bytes(void);
+MK36_API int mk36_comm_buffer_alloc(void** buffer);
+MK36_API int mk36_comm_buffer_free(void* buffer);
+MK36_API int mk36_ipc_export(void* buffer, unsigned char handle[MK36_IPC_HANDLE_BYTES]);
+MK36_API int mk36_ipc_open(const unsigned char handle[MK36_IPC_HANDLE_BYTES], void** buffer);
+MK36_API int mk36_ipc_close(void* buffer);
+MK36_API int mk36_moe_decode_ep(const mk36_moe_args* args, const mk36_comm* comm, void* workspace,
+                                size_t workspace_bytes, void* stream);
+MK36_API int mk36_dense_ffn_decode_tp(const mk36_dense_ffn_args* args, const mk36_comm* comm, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

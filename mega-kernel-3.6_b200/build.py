@@ -29,6 +29,7 @@ INCLUDE = ROOT / "include"
 
 CUDA_SOURCES = [
     "mk36_api.cu",
+    "mk36_comm.cu",
     "moe_decode.cu",
     "moe_decode_ring.cu",
     "dense_ffn_decode.cu",

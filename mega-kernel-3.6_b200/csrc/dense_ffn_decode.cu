@@ -7,7 +7,7 @@
 #include "mk36_common.cuh"
 
 namespace mk36 {
-int moe_decode_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 }
 
 using namespace mk36;
@@ -52,7 +52,16 @@ int mk36_dense_ffn_decode(const mk36_dense_ffn_args* args, void* workspace, size
     mk36_moe_args m;
     int rc = to_moe_args(args, &m);
     if (rc != MK36_OK) return rc;
-    return moe_decode_launch(&m, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    return moe_decode_launch(&m, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int mk36_dense_ffn_decode_tp(const mk36_dense_ffn_args* args, const mk36_comm* comm, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    if (!comm) MK36_FAIL(MK36_ERR_INVALID_ARG, "dense_ffn_decode_tp: comm is NULL");
+    mk36_moe_args m;
+    int rc = to_moe_args(args, &m);
+    if (rc != MK36_OK) return rc;
+    return moe_decode_launch(&m, comm, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

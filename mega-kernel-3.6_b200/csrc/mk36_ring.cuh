@@ -1,4 +1,4 @@
-// Shared-memory ring fed by the bulk-copy engine (TMA, 1-D cp.async.bulk, no multicast) and
+// Shared-memory ring fed by the bulk-copy engine (TMA, 1-D cp.async.bulk into the issuing CTA only) and
 // drained by compute warps: mbarrier wrappers with bounded waits, and the copy itself.
 //
 // A stage is a fixed-size slot of shared memory with two mbarriers: `full` (armed by the producer

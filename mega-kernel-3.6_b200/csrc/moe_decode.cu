@@ -18,6 +18,7 @@
 #include <cfloat>
 #include <climits>
 
+#include "mk36_comm.cuh"
 #include "mk36_common.cuh"
 
 namespace mk36 {
@@ -53,6 +54,7 @@ struct MoeParams {
     float eps;
     // dynamic shared memory layout (byte offsets)
     int off_logits, off_mask, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w;
+    CommParams comm;  // world > 1: the epilogue sums the ranks' partial outputs over peer memory
 };
 
 // dot products of one weight row with NT activation vectors held in shared memory (split layout)
@@ -150,12 +152,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_flag;
     __shared__ int s_unique;
+    __shared__ unsigned s_step;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const int ncta = gridDim.x;
     const int cta = blockIdx.x;
+    const bool exchange = p.comm.world > 1;
+    if (tid == 0) s_step = exchange ? comm_read_step(p.comm) : 0u;
 
     const int Hc = (p.H + 7) >> 3;        // chunks per hidden vector
     const int x_half = Hc * 4;            // floats per half of the split layout
@@ -516,7 +521,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
 #pragma unroll
                 for (int t = 0; t < TB; ++t) {
                     if (t < p.ntok) {
-                        if (p.partial_out) {
+                        if (exchange) {
+                            const int parity = (int)(s_step & 1u);
+                            for (int q = 0; q < p.comm.world; ++q)
+                                comm_slot(comm_buf(p.comm, q), parity, p.comm.rank)[(size_t)t * p.H + h] = acc[t];
+                        } else if (p.partial_out) {
                             p.partial_out[(size_t)t * p.H + h] = acc[t];
                         } else {
                             float v = acc[t];
@@ -529,6 +538,29 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
         }
     }
     __syncthreads();
+    if (exchange) {
+        // every rank now holds this CTA's rows of every rank's partial sum: add them in rank order
+        const unsigned step = s_step;
+        const int parity = (int)(step & 1u);
+        if (tid == 0) {
+            comm_signal(p.comm, parity, cta, step + 1u);
+            s_flag = comm_wait(p.comm, p.ctl, parity, cta, step + 1u) ? 1 : 0;
+            if (cta == 0 && s_flag) comm_write_step(p.comm, step + 1u);
+        }
+        __syncthreads();
+        if (!s_flag) return;
+        const int h0 = (int)(((long long)p.H * cta) / ncta);
+        const int h1 = (int)(((long long)p.H * (cta + 1)) / ncta);
+        T* out = static_cast<T*>(p.out);
+        for (int t = 0; t < p.ntok; ++t) {
+            for (int h = h0 + tid; h < h1; h += kMoeThreads) {
+                const size_t o = (size_t)t * p.H + h;
+                float v = comm_sum(p.comm, parity, o);
+                if (p.add_residual) v += to_float<T>(x[o]);
+                out[o] = from_float<T>(v);
+            }
+        }
+    }
     if (tracer) trace_stamp(p.ctl, 9);
 }
 
@@ -619,14 +651,18 @@ const void* moe_kernel(int dtype, int tb) {
 
 }  // namespace
 
-int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled);
+int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                           bool* handled);
 
-int moe_decode_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+// `comm` (may be null) makes the kernels end with the cross-GPU sum of the ranks' partial outputs.
+int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int rc = check_moe_args(a);
     if (rc != MK36_OK) return rc;
+    if (comm && comm->world > 1 && (!a->out || a->partial_out))
+        MK36_FAIL(MK36_ERR_INVALID_ARG, "moe_decode: the multi-GPU entry points write `out` and take no partial_out");
     if (!options().force_generic) {
         bool handled = false;
-        rc = moe_decode_ring_launch(a, workspace, workspace_bytes, stream, &handled);
+        rc = moe_decode_ring_launch(a, comm, workspace, workspace_bytes, stream, &handled);
         if (rc != MK36_OK || handled) return rc;
     }
     const DeviceInfo* dev = current_device_info();
@@ -644,6 +680,8 @@ int moe_decode_launch(const mk36_moe_args* a, void* workspace, size_t workspace_
     const size_t es = elem_size(a->dtype);
     const int per8 = 8;
     MoeParams p;
+    rc = comm_params_from(comm, a->hidden, &p.comm, "moe_decode");
+    if (rc != MK36_OK) return rc;
     p.norm_w = a->norm_weight;
     p.router_w = a->router_weight;
     p.egate = a->expert_gate;
@@ -713,7 +751,12 @@ size_t mk36_moe_workspace_bytes(const mk36_moe_args* a) {
 }
 
 int mk36_moe_decode(const mk36_moe_args* args, void* workspace, size_t workspace_bytes, void* stream) {
-    return moe_decode_launch(args, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    return moe_decode_launch(args, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int mk36_moe_decode_ep(const mk36_moe_args* args, const mk36_comm* comm, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!comm) MK36_FAIL(MK36_ERR_INVALID_ARG, "moe_decode_ep: comm is NULL");
+    return moe_decode_launch(args, comm, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

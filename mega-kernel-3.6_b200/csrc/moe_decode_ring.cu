@@ -5,7 +5,7 @@
 // work per weight element is as expensive as streaming it.  So
 //   * the weights do not go through registers on their way from HBM: one producer lane feeds a
 //     shared-memory ring of 32 KB stages with 1-D bulk copies (cp.async.bulk completing on
-//     mbarriers, no multicast).  Weight addresses depend only on the routing decision, so the
+//     mbarriers, each copy into the issuing CTA only).  Weight addresses depend only on the routing decision, so the
 //     producer runs ahead of the grid barriers: router rows, shared-expert rows and the CTA's
 //     slice of shared_down are requested at kernel entry, before the token is even normalised,
 //     and once the top-k is known the routed gate/up rows and then the routed down rows are
@@ -30,6 +30,7 @@
 #include <cfloat>
 #include <climits>
 
+#include "mk36_comm.cuh"
 #include "mk36_ring.cuh"
 
 namespace mk36 {
@@ -77,6 +78,7 @@ struct MoeRingParams {
     FastDiv fd_ncta, fd_rows_h, fd_pr, fd_I, fd_K, fd_qi, fd_qis, fd_epc;
     // byte offsets into dynamic shared memory
     int off_ring, off_sdown, off_act, off_part, off_red, off_logits, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
+    CommParams comm;  // world > 1: the epilogue sums the ranks' partial outputs over peer memory
 };
 
 __device__ __forceinline__ int chunks_in(int r0, int r1, const FastDiv& per) {
@@ -231,6 +233,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     __shared__ int s_unique;
     __shared__ int s_abort;
     __shared__ float s_red[kRingConsumerWarps];
+    __shared__ unsigned s_step;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -283,6 +286,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     if (tid == 0) {
         s_abort = 0;
+        s_step = (p.comm.world > 1) ? comm_read_step(p.comm) : 0u;
         for (int s = 0; s < kRingMaxStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kRingGroupWarps);
@@ -810,6 +814,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     // ---- combine in slot order, add the residual, round once ----
     T* out = static_cast<T*>(p.out);
+    const bool exchange = p.comm.world > 1;
+    const unsigned step = s_step;
+    const int parity = (int)(step & 1u);
     for (int idx = tid; idx < p.ntok * kRingTileRows; idx += kRingConsumerThreads) {
         const int b = idx >> 4, j = idx & (kRingTileRows - 1);
         if (j >= hr) continue;
@@ -821,9 +828,30 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
         if (p.Is > 0) v += part[(npairs + b) * p.hr_max + j];
         const size_t o = (size_t)b * p.H + h0 + j;
-        if (p.partial_out) {
+        if (exchange) {
+            for (int q = 0; q < p.comm.world; ++q) comm_slot(comm_buf(p.comm, q), parity, p.comm.rank)[o] = v;
+        } else if (p.partial_out) {
             p.partial_out[o] = v;
         } else {
+            if (p.add_residual) v += to_float<T>(x[o]);
+            out[o] = from_float<T>(v);
+        }
+    }
+    if (exchange) {
+        // every rank now holds this CTA's rows of every rank's partial sum: add them in rank order
+        named_barrier(1, kRingConsumerThreads);
+        if (tid == 0) {
+            comm_signal(p.comm, parity, cta, step + 1u);
+            s_flag = comm_wait(p.comm, p.ctl, parity, cta, step + 1u) ? 1 : 0;
+            if (cta == 0 && s_flag) comm_write_step(p.comm, step + 1u);
+        }
+        named_barrier(1, kRingConsumerThreads);
+        if (!s_flag) return;
+        for (int idx = tid; idx < p.ntok * kRingTileRows; idx += kRingConsumerThreads) {
+            const int b = idx >> 4, j = idx & (kRingTileRows - 1);
+            if (j >= hr) continue;
+            const size_t o = (size_t)b * p.H + h0 + j;
+            float v = comm_sum(p.comm, parity, o);
             if (p.add_residual) v += to_float<T>(x[o]);
             out[o] = from_float<T>(v);
         }
@@ -837,7 +865,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
 // Launches the streaming variant when the shapes suit it and sets *handled; otherwise leaves
 // *handled false (no error) so that the caller uses the general kernel.
-int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled) {
+int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                           bool* handled) {
     *handled = false;
     if (a->dtype != MK36_BF16 && a->dtype != MK36_F16) return MK36_OK;
     const int H = a->hidden, E = a->experts, K = a->top_k, I = a->intermediate, Is = a->shared_intermediate;
@@ -873,6 +902,10 @@ int moe_decode_ring_launch(const mk36_moe_args* a, void* workspace, size_t works
     }
 
     MoeRingParams p;
+    {
+        const int rc = comm_params_from(comm, H, &p.comm, "moe_decode");
+        if (rc != MK36_OK) return rc;
+    }
     size_t off = 0;
     auto take = [&](size_t bytes, size_t align) {
         off = align_up(off, align);

@@ -186,6 +186,69 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> moe_decode_partial(
     return std::make_tuple(partial, indices, weights);
 }
 
+// Descriptor of the exchange buffers from Python integers (device pointers as mapped here).
+mk36_comm comm_from(int64_t rank, int64_t world, const std::vector<int64_t>& buffers) {
+    TORCH_CHECK(world >= 1 && world <= MK36_MAX_RANKS, "world size must be in [1, ", MK36_MAX_RANKS, "]");
+    TORCH_CHECK(rank >= 0 && rank < world, "rank outside [0, world)");
+    TORCH_CHECK(static_cast<int64_t>(buffers.size()) == world, "one exchange buffer pointer per rank is required");
+    mk36_comm c{};
+    c.rank = static_cast<int32_t>(rank);
+    c.world = static_cast<int32_t>(world);
+    for (int64_t q = 0; q < world; ++q) c.buffers[q] = reinterpret_cast<void*>(static_cast<uintptr_t>(buffers[q]));
+    return c;
+}
+
+// Expert-parallel MoE step that ends, inside the kernel, with the sum over the ranks, the residual
+// and the rounding: every rank returns the full output.
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> moe_decode_ep(
+    torch::Tensor x, torch::Tensor norm_weight, torch::Tensor router_weight, torch::Tensor expert_gate, torch::Tensor expert_up,
+    torch::Tensor expert_down, torch::Tensor shared_gate, torch::Tensor shared_up, torch::Tensor shared_down, double eps,
+    int64_t top_k, bool add_residual, int64_t expert_base, int64_t rank, int64_t world, std::vector<int64_t> buffers) {
+    check_moe_tensors(x, norm_weight, router_weight, expert_gate, expert_up, expert_down, shared_gate, shared_up, shared_down,
+                      top_k, expert_gate.size(0));
+    TORCH_CHECK(expert_base >= 0 && expert_base + expert_gate.size(0) <= router_weight.size(0),
+                "local expert range is outside the router's experts");
+    const c10::cuda::CUDAGuard guard(x.device());
+    mk36_moe_args a =
+        moe_args(x, norm_weight, router_weight, expert_gate, expert_up, expert_down, shared_gate, shared_up, shared_down, eps,
+                 top_k, add_residual);
+    a.expert_base = static_cast<int32_t>(expert_base);
+    a.local_experts = static_cast<int32_t>(expert_gate.size(0));
+    const mk36_comm c = comm_from(rank, world, buffers);
+    auto out = torch::empty_like(x);
+    auto indices = torch::empty({x.size(0), top_k}, x.options().dtype(torch::kInt64));
+    auto weights = torch::empty({x.size(0), top_k}, x.options().dtype(torch::kFloat32));
+    a.out = out.data_ptr();
+    a.indices = indices.data_ptr<int64_t>();
+    a.route_weights = weights.data_ptr<float>();
+    Workspace& ws = workspace_for(x, mk36_moe_workspace_bytes(&a));
+    check_rc(mk36_moe_decode_ep(&a, &c, ws.buffer.data_ptr(), ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    return std::make_tuple(out, indices, weights);
+}
+
+int64_t comm_buffer_alloc() {
+    void* p = nullptr;
+    check_rc(mk36_comm_buffer_alloc(&p));
+    return static_cast<int64_t>(reinterpret_cast<uintptr_t>(p));
+}
+
+void comm_buffer_free(int64_t ptr) { check_rc(mk36_comm_buffer_free(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)))); }
+
+py::bytes ipc_export(int64_t ptr) {
+    unsigned char h[MK36_IPC_HANDLE_BYTES];
+    check_rc(mk36_ipc_export(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)), h));
+    return py::bytes(reinterpret_cast<const char*>(h), MK36_IPC_HANDLE_BYTES);
+}
+
+int64_t ipc_open(const std::string& handle) {
+    TORCH_CHECK(handle.size() == MK36_IPC_HANDLE_BYTES, "an IPC handle has ", MK36_IPC_HANDLE_BYTES, " bytes");
+    void* p = nullptr;
+    check_rc(mk36_ipc_open(reinterpret_cast<const unsigned char*>(handle.data()), &p));
+    return static_cast<int64_t>(reinterpret_cast<uintptr_t>(p));
+}
+
+void ipc_close(int64_t ptr) { check_rc(mk36_ipc_close(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)))); }
+
 // -------------------------------------------------------------------------------------------
 // dense_ffn_decode (no counterpart in csrc/bindings.cpp; replaces ops.py:202-218)
 // -------------------------------------------------------------------------------------------
@@ -213,7 +276,7 @@ void check_dense_tensors(const torch::Tensor& x, const torch::Tensor& norm_weigh
 
 torch::Tensor dense_ffn_impl(const torch::Tensor& x, const torch::Tensor& norm_weight, const torch::Tensor& gate_weight,
                              const torch::Tensor& up_weight, const torch::Tensor& down_weight, double eps, bool add_residual,
-                             bool partial) {
+                             bool partial, const mk36_comm* comm = nullptr) {
     check_dense_tensors(x, norm_weight, gate_weight, up_weight, down_weight);
     const c10::cuda::CUDAGuard guard(x.device());
     mk36_dense_ffn_args a{};
@@ -237,8 +300,18 @@ torch::Tensor dense_ffn_impl(const torch::Tensor& x, const torch::Tensor& norm_w
         a.out = out.data_ptr();
     }
     Workspace& ws = workspace_for(x, mk36_dense_ffn_workspace_bytes(&a));
-    check_rc(mk36_dense_ffn_decode(&a, ws.buffer.data_ptr(), ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    if (comm) check_rc(mk36_dense_ffn_decode_tp(&a, comm, ws.buffer.data_ptr(), ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    else check_rc(mk36_dense_ffn_decode(&a, ws.buffer.data_ptr(), ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
     return out;
+}
+
+// Tensor-parallel dense FFN step (this rank's gate/up rows and down columns) that ends with the sum
+// over the ranks inside the kernel.
+torch::Tensor dense_ffn_decode_tp(torch::Tensor x, torch::Tensor norm_weight, torch::Tensor gate_weight, torch::Tensor up_weight,
+                                  torch::Tensor down_weight, double eps, bool add_residual, int64_t rank, int64_t world,
+                                  std::vector<int64_t> buffers) {
+    const mk36_comm c = comm_from(rank, world, buffers);
+    return dense_ffn_impl(x, norm_weight, gate_weight, up_weight, down_weight, eps, add_residual, false, &c);
 }
 
 torch::Tensor dense_ffn_decode(torch::Tensor x, torch::Tensor norm_weight, torch::Tensor gate_weight, torch::Tensor up_weight,
@@ -386,6 +459,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_decode_partial", &moe_decode_partial, "expert-parallel partial of the MoE decode kernel");
     m.def("dense_ffn_decode", &dense_ffn_decode, "Qwen3.6 dense SwiGLU FFN decode kernel (sm_100a)");
     m.def("dense_ffn_decode_partial", &dense_ffn_decode_partial, "tensor-parallel partial of the dense FFN decode kernel");
+    m.def("moe_decode_ep", &moe_decode_ep, "expert-parallel MoE decode with the cross-GPU sum fused into the kernel");
+    m.def("dense_ffn_decode_tp", &dense_ffn_decode_tp, "tensor-parallel dense FFN decode with the cross-GPU sum fused into the kernel");
+    m.def("comm_buffer_alloc", &comm_buffer_alloc, "allocate and clear this rank's exchange buffer; returns its device pointer");
+    m.def("comm_buffer_free", &comm_buffer_free);
+    m.def("ipc_export", &ipc_export, "CUDA IPC handle of an exchange buffer");
+    m.def("ipc_open", &ipc_open, "map a peer's exchange buffer; returns the device pointer in this process");
+    m.def("ipc_close", &ipc_close);
     m.def("full_attention_decode", &full_attention_decode, "Qwen3.6 full-attention decode kernel (sm_100a)");
     m.def("linear_attention_decode", &linear_attention_decode, "Qwen3.6 linear-attention recurrent decode kernel (sm_100a)");
     m.def("linear_attention_decode_ex", &linear_attention_decode_ex, "per-head decay/beta, grouped keys, optional in-place state",

@@ -61,6 +61,14 @@ class LinearAttentionArgs(C.Structure):
     ]
 
 
+MK36_MAX_RANKS = 8
+MK36_IPC_HANDLE_BYTES = 64
+
+
+class Comm(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("buffers", C.c_void_p * MK36_MAX_RANKS)]
+
+
 # symbol -> (restype, argtypes); every function declared in mk36.h appears here
 SIGNATURES = {
     "mk36_version": (C.c_int, []),
@@ -80,6 +88,14 @@ SIGNATURES = {
     "mk36_full_attention_decode": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_full_attention_decode_static": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
     "mk36_linear_attention_decode": (C.c_int, [C.POINTER(LinearAttentionArgs), C.c_void_p]),
+    "mk36_comm_buffer_bytes": (C.c_size_t, []),
+    "mk36_comm_buffer_alloc": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "mk36_comm_buffer_free": (C.c_int, [C.c_void_p]),
+    "mk36_ipc_export": (C.c_int, [C.c_void_p, C.POINTER(C.c_ubyte)]),
+    "mk36_ipc_open": (C.c_int, [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)]),
+    "mk36_ipc_close": (C.c_int, [C.c_void_p]),
+    "mk36_moe_decode_ep": (C.c_int, [C.POINTER(MoeArgs), C.POINTER(Comm), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mk36_dense_ffn_decode_tp": (C.c_int, [C.POINTER(DenseFfnArgs), C.POINTER(Comm), C.c_void_p, C.c_size_t, C.c_void_p]),
 }
 
 

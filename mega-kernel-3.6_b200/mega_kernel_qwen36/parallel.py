@@ -13,9 +13,12 @@ is nothing to mirror here.  Three partitions follow the structure of the ops:
   * attention - KV-head parallel.  Rank r owns KV heads [r*Hkv/N, ...) and their query heads; no
     exchange is needed, an all-gather only if every rank wants the full output.
 
-The collective is NCCL through ``torch.distributed`` (gloo on CPU for tests).  The partial sums
-leave the kernels in fp32 and are reduced in fp32, so the result does not depend on the number
-of ranks beyond fp32 reassociation.
+Two ways to sum the partials.  The plain one is an all-reduce through ``torch.distributed``
+(NCCL on GPUs, gloo on CPU for tests) followed by the residual add.  The fast one is
+``PeerExchange``: the kernels themselves store their partial rows into every rank's exchange
+buffer over NVLink, signal, wait (bounded) for the peers' rows and finish the output in the same
+launch, so a decode step stays one kernel per GPU (``exchange=`` argument below).  The partial
+sums are fp32 and are added in rank order on every rank, so all ranks get bit-identical outputs.
 """
 
 from __future__ import annotations
@@ -91,6 +94,51 @@ def shard_attention_inputs(inputs: FullAttentionInputs, rank: int, world: int) -
     )
 
 
+class PeerExchange:
+    """The ranks' exchange buffers for the fused cross-GPU sum (see csrc/mk36_comm.cuh).
+
+    Collective constructor: every rank of `group` calls it once, with its CUDA device current.
+    It allocates this rank's buffer (a plain cudaMalloc: CUDA IPC cannot export a slice of a
+    caching allocator's block), swaps IPC handles through the process group and maps the peers'
+    buffers.  All ranks must then make the same sequence of ``moe_decode_ep`` /
+    ``dense_ffn_decode_tp`` calls with this object.
+    """
+
+    def __init__(self, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        from .ops import _C
+
+        if _C is None:
+            raise RuntimeError("the sm_100a extension is not built; there is no fallback for the peer exchange")
+        self._ext = _C
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device(device)
+        self._own = 0
+        self._peers = {}
+        with torch.cuda.device(self.device):
+            self._own = int(_C.comm_buffer_alloc())
+            handle = bytes(_C.ipc_export(self._own))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+            for q, h in enumerate(handles):
+                if q != self.rank:
+                    self._peers[q] = int(_C.ipc_open(h))
+        self.buffers = [self._own if q == self.rank else self._peers[q] for q in range(self.world)]
+        dist.barrier(group=group)  # every buffer is cleared and mapped everywhere before the first step
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees the own one.  Collective in spirit: no rank may still
+        be inside a step that uses this object."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for ptr in self._peers.values():
+                self._ext.ipc_close(ptr)
+            self._peers = {}
+            if self._own:
+                self._ext.comm_buffer_free(self._own)
+                self._own = 0
+
+
 def combine_partials(partial: torch.Tensor, x: torch.Tensor, *, add_residual: bool = True,
                      group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Sums the ranks' fp32 partials [B, H] in place (all-reduce), adds the residual once and
@@ -105,22 +153,30 @@ def combine_partials(partial: torch.Tensor, x: torch.Tensor, *, add_residual: bo
 
 
 def moe_decode_ep(x: torch.Tensor, shard: MoeShard, *, eps: float = 1e-6, top_k: int = 8, add_residual: bool = True,
-                  group: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                  group: Optional[dist.ProcessGroup] = None,
+                  exchange: Optional[PeerExchange] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Expert-parallel ``moe_decode``: x is replicated on every rank; returns the full output on
-    every rank plus the (identical on all ranks) routing."""
+    every rank plus the (identical on all ranks) routing.  With ``exchange`` the sum over the
+    ranks happens inside the kernel (one launch per step); without it, through an all-reduce."""
     w = shard.weights
     tensors = (x, w.norm_weight, w.router_weight, w.expert_gate, w.expert_up, w.expert_down,
                w.shared_gate, w.shared_up, w.shared_down)
     ext = _native("moe_decode_ep", *tensors)
+    if exchange is not None:
+        return ext.moe_decode_ep(*tensors, float(eps), int(top_k), bool(add_residual), int(shard.expert_base),
+                                 exchange.rank, exchange.world, exchange.buffers)
     partial, idx, rw = ext.moe_decode_partial(*tensors, float(eps), int(top_k), int(shard.expert_base))
     return combine_partials(partial, x, add_residual=add_residual, group=group), idx, rw
 
 
 def dense_ffn_decode_tp(x: torch.Tensor, local: DenseFfnWeights, *, eps: float = 1e-6, add_residual: bool = True,
-                        group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """Tensor-parallel ``dense_ffn_decode``: one all-reduce of the fp32 partial."""
+                        group: Optional[dist.ProcessGroup] = None, exchange: Optional[PeerExchange] = None) -> torch.Tensor:
+    """Tensor-parallel ``dense_ffn_decode``: the fp32 partials are summed inside the kernel
+    (``exchange``) or by one all-reduce."""
     tensors = (x, local.norm_weight, local.gate_weight, local.up_weight, local.down_weight)
     ext = _native("dense_ffn_decode_tp", *tensors)
+    if exchange is not None:
+        return ext.dense_ffn_decode_tp(*tensors, float(eps), bool(add_residual), exchange.rank, exchange.world, exchange.buffers)
     partial = ext.dense_ffn_decode_partial(*tensors, float(eps))
     return combine_partials(partial, x, add_residual=add_residual, group=group)
 
