@@ -2,25 +2,25 @@
 // the epilogue of the decode kernels instead of a separate collective launch.
 //
 // Every rank owns one exchange buffer; every rank maps all buffers (own: plain device pointer,
-// peers: CUDA IPC mappings).  A step of the expert-parallel MoE / tensor-parallel dense FFN ends
-// like this in each CTA, for the output rows that CTA owns:
+// peers: CUDA IPC mappings).  A partial value travels together with the number of the step it
+// belongs to, as one aligned 64-bit word {value, step + 1}: a 64-bit store is a single access, so
+// whoever reads the word sees either the old pair or the new pair, never a mix, and the word is
+// its own "ready" flag.  No fence, no separate flag and no barrier is needed, and the cost of the
+// exchange is one NVLink store latency.  Per output element o of the rows a CTA owns:
 //
-//   1. store its partial values into slot[parity][own rank] of EVERY rank's buffer (plain peer
-//      stores over NVLink; its own buffer included),
-//   2. CTA barrier, then one thread: system-scope fence and a release store of step+1 into
-//      flag[parity][own rank][cta] of every rank's buffer,
-//   3. the same thread waits (bounded) until flag[parity][q][cta] of its OWN buffer equals step+1
-//      for every rank q, CTA barrier,
-//   4. sum slot[parity][q] over q in rank order from its own buffer (L2 loads), add the residual,
-//      round, store.  The order is fixed, so all ranks produce bit-identical outputs.
+//   put:  store {v, step + 1} into slot[parity][own rank][o] of EVERY rank's buffer (own included);
+//   get:  for q = 0 .. world-1, in rank order: poll slot[parity][q][o] of the OWN buffer until its
+//         tag is step + 1 (bounded), add the value.  Then residual, rounding, store.
+//
+// The order of the sum is fixed, so all ranks produce bit-identical outputs.
 //
 // `step` is a counter kept in the rank's own buffer and advanced by the kernel, so a captured CUDA
-// graph can be replayed.  parity = step & 1 alternates between two sets of slots and flags: a rank
-// can run at most one step ahead of the slowest one (it needs everyone's contribution to finish a
-// step), so two sets are enough to keep a fast rank from overwriting what a slow one still reads.
-// All ranks must make the same sequence of calls with the same shapes (same grid, same rows per
-// CTA); a rank that never shows up makes the others' waits run out, which sets the status word
-// and ends the kernel - nothing spins forever.
+// graph can be replayed.  parity = step & 1 alternates between two sets of slots: a rank can run at
+// most one step ahead of the slowest one (it needs everyone's contribution to finish a step), so
+// two sets are enough to keep a fast rank from overwriting what a slow one still has to read.
+// All ranks must make the same sequence of calls with the same shapes.  A rank that never shows up
+// makes the others' polls run out, which sets the status word and ends the kernel - nothing spins
+// forever.
 //
 // Peer memory is touched with plain ld/st instructions only (no bulk copies, no switch reductions).
 #pragma once
@@ -30,12 +30,10 @@
 namespace mk36 {
 
 constexpr int kCommMaxRanks = MK36_MAX_RANKS;
-constexpr int kCommMaxCtas = 1024;             // flags per (parity, source rank)
-constexpr int kCommMaxElems = 8 * 8192;        // fp32 values per (parity, source rank): 8 tokens x hidden <= 8192
+constexpr int kCommMaxElems = 8 * 8192;        // values per (parity, source rank): 8 tokens x hidden <= 8192
 constexpr size_t kCommHeaderBytes = 4096;      // step counter
-constexpr size_t kCommFlagBytes = (size_t)2 * kCommMaxRanks * kCommMaxCtas * 4;
-constexpr size_t kCommSlotBytes = (size_t)2 * kCommMaxRanks * kCommMaxElems * 4;
-constexpr size_t kCommBytes = kCommHeaderBytes + kCommFlagBytes + kCommSlotBytes;
+constexpr size_t kCommSlotBytes = (size_t)2 * kCommMaxRanks * kCommMaxElems * 8;
+constexpr size_t kCommBytes = kCommHeaderBytes + kCommSlotBytes;
 constexpr int kStatusCommWait = 401;           // a peer's contribution never arrived
 constexpr unsigned long long kCommWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
@@ -63,12 +61,8 @@ __device__ __forceinline__ unsigned char* comm_buf(const CommParams& c, int q) {
 
 __device__ __forceinline__ unsigned* comm_step_ptr(unsigned char* base) { return reinterpret_cast<unsigned*>(base); }
 
-__device__ __forceinline__ unsigned* comm_flag(unsigned char* base, int parity, int src, int cta) {
-    return reinterpret_cast<unsigned*>(base + kCommHeaderBytes) + ((size_t)(parity * kCommMaxRanks + src) * kCommMaxCtas + cta);
-}
-
-__device__ __forceinline__ float* comm_slot(unsigned char* base, int parity, int src) {
-    return reinterpret_cast<float*>(base + kCommHeaderBytes + kCommFlagBytes) + (size_t)(parity * kCommMaxRanks + src) * kCommMaxElems;
+__device__ __forceinline__ unsigned long long* comm_slot(unsigned char* base, int parity, int src) {
+    return reinterpret_cast<unsigned long long*>(base + kCommHeaderBytes) + (size_t)(parity * kCommMaxRanks + src) * kCommMaxElems;
 }
 
 __device__ __forceinline__ unsigned comm_read_step(const CommParams& c) {
@@ -81,46 +75,51 @@ __device__ __forceinline__ void comm_write_step(const CommParams& c, unsigned v)
     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(comm_step_ptr(comm_buf(c, c.rank))), "r"(v) : "memory");
 }
 
-// One thread, after a CTA-wide barrier that follows the partial stores of the whole CTA.
-__device__ __forceinline__ void comm_signal(const CommParams& c, int parity, int cta, unsigned value) {
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
+// Sends element `idx` of this rank's partial sum for step `step` to every rank.
+__device__ __forceinline__ void comm_put(const CommParams& c, unsigned step, size_t idx, float v) {
+    const unsigned long long word = ((unsigned long long)(step + 1u) << 32) | (unsigned long long)__float_as_uint(v);
+    const int parity = (int)(step & 1u);
     for (int q = 0; q < c.world; ++q) {
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(comm_flag(comm_buf(c, q), parity, c.rank, cta)), "r"(value) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(comm_slot(comm_buf(c, q), parity, c.rank) + idx), "l"(word) : "memory");
     }
 }
 
-// One thread.  Returns false (and records the status code) when a contribution does not arrive
-// within the limit.
-static __device__ __noinline__ bool comm_wait_on(unsigned char* own, int world, Control* ctl, int parity, int cta, unsigned value) {
+// Out of line and fed with plain values: a reference to the kernel parameters would force a copy of
+// the parameter block into local memory.  Returns false when the word never shows up.
+static __device__ __noinline__ bool comm_poll_slow(const unsigned long long* addr, unsigned tag, Control* ctl, unsigned long long* word) {
     const unsigned long long t0 = global_timer_ns();
-    for (int q = 0; q < world; ++q) {
-        const unsigned* f = comm_flag(own, parity, q, cta);
-        unsigned spins = 0;
-        for (;;) {
-            unsigned v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if (v == value) break;
-            if ((++spins & 63u) == 0u && global_timer_ns() - t0 > kCommWaitLimitNs) {
-                atomicCAS(&ctl->status, 0, kStatusCommWait);
-                return false;
-            }
+    unsigned spins = 0;
+    for (;;) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(addr) : "memory");
+        if ((unsigned)(w >> 32) == tag) {
+            *word = w;
+            return true;
+        }
+        if ((++spins & 63u) == 0u && global_timer_ns() - t0 > kCommWaitLimitNs) {
+            atomicCAS(&ctl->status, 0, kStatusCommWait);
+            return false;
         }
     }
-    return true;
 }
 
-// (The out-of-line part takes plain values: a reference to the kernel parameters would force a copy of
-// the parameter block into local memory.)
-__device__ __forceinline__ bool comm_wait(const CommParams& c, Control* ctl, int parity, int cta, unsigned value) {
-    return comm_wait_on(comm_buf(c, c.rank), c.world, ctl, parity, cta, value);
-}
-
-// Sum over the ranks, in rank order, of element `idx` of this step's slots in the own buffer.
-__device__ __forceinline__ float comm_sum(const CommParams& c, int parity, size_t idx) {
-    float v = 0.0f;
+// Sum over the ranks, in rank order, of element `idx` for step `step`; waits (bounded) for
+// contributions that have not arrived yet.  Returns false when one never arrives.
+__device__ __forceinline__ bool comm_get_sum(const CommParams& c, Control* ctl, unsigned step, size_t idx, float* sum) {
+    const int parity = (int)(step & 1u);
     unsigned char* own = comm_buf(c, c.rank);
-    for (int q = 0; q < c.world; ++q) v += __ldcg(comm_slot(own, parity, q) + idx);
-    return v;
+    float v = 0.0f;
+    for (int q = 0; q < c.world; ++q) {
+        const unsigned long long* addr = comm_slot(own, parity, q) + idx;
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(addr) : "memory");
+        if ((unsigned)(w >> 32) != step + 1u) {
+            if (!comm_poll_slow(addr, step + 1u, ctl, &w)) return false;
+        }
+        v += __uint_as_float((unsigned)w);
+    }
+    *sum = v;
+    return true;
 }
 
 #endif  // __CUDACC__

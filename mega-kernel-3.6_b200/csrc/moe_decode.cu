@@ -522,9 +522,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
                 for (int t = 0; t < TB; ++t) {
                     if (t < p.ntok) {
                         if (exchange) {
-                            const int parity = (int)(s_step & 1u);
-                            for (int q = 0; q < p.comm.world; ++q)
-                                comm_slot(comm_buf(p.comm, q), parity, p.comm.rank)[(size_t)t * p.H + h] = acc[t];
+                            comm_put(p.comm, s_step, (size_t)t * p.H + h, acc[t]);
                         } else if (p.partial_out) {
                             p.partial_out[(size_t)t * p.H + h] = acc[t];
                         } else {
@@ -539,27 +537,22 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_decode_kernel(const MoePar
     }
     __syncthreads();
     if (exchange) {
-        // every rank now holds this CTA's rows of every rank's partial sum: add them in rank order
+        // collect the ranks' shares of this CTA's rows, in rank order (each element is its own flag)
         const unsigned step = s_step;
-        const int parity = (int)(step & 1u);
-        if (tid == 0) {
-            comm_signal(p.comm, parity, cta, step + 1u);
-            s_flag = comm_wait(p.comm, p.ctl, parity, cta, step + 1u) ? 1 : 0;
-            if (cta == 0 && s_flag) comm_write_step(p.comm, step + 1u);
-        }
-        __syncthreads();
-        if (!s_flag) return;
         const int h0 = (int)(((long long)p.H * cta) / ncta);
         const int h1 = (int)(((long long)p.H * (cta + 1)) / ncta);
         T* out = static_cast<T*>(p.out);
         for (int t = 0; t < p.ntok; ++t) {
             for (int h = h0 + tid; h < h1; h += kMoeThreads) {
                 const size_t o = (size_t)t * p.H + h;
-                float v = comm_sum(p.comm, parity, o);
+                float v;
+                if (!comm_get_sum(p.comm, p.ctl, step, o, &v)) continue;
                 if (p.add_residual) v += to_float<T>(x[o]);
                 out[o] = from_float<T>(v);
             }
         }
+        // every CTA read the counter at entry, before the grid barrier
+        if (cta == 0 && tid == 0) comm_write_step(p.comm, step + 1u);
     }
     if (tracer) trace_stamp(p.ctl, 9);
 }

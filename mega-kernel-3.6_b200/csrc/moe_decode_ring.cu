@@ -816,7 +816,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     T* out = static_cast<T*>(p.out);
     const bool exchange = p.comm.world > 1;
     const unsigned step = s_step;
-    const int parity = (int)(step & 1u);
     for (int idx = tid; idx < p.ntok * kRingTileRows; idx += kRingConsumerThreads) {
         const int b = idx >> 4, j = idx & (kRingTileRows - 1);
         if (j >= hr) continue;
@@ -829,7 +828,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         if (p.Is > 0) v += part[(npairs + b) * p.hr_max + j];
         const size_t o = (size_t)b * p.H + h0 + j;
         if (exchange) {
-            for (int q = 0; q < p.comm.world; ++q) comm_slot(comm_buf(p.comm, q), parity, p.comm.rank)[o] = v;
+            comm_put(p.comm, step, o, v);  // this rank's share of element o, to every rank
         } else if (p.partial_out) {
             p.partial_out[o] = v;
         } else {
@@ -838,23 +837,18 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
     }
     if (exchange) {
-        // every rank now holds this CTA's rows of every rank's partial sum: add them in rank order
-        named_barrier(1, kRingConsumerThreads);
-        if (tid == 0) {
-            comm_signal(p.comm, parity, cta, step + 1u);
-            s_flag = comm_wait(p.comm, p.ctl, parity, cta, step + 1u) ? 1 : 0;
-            if (cta == 0 && s_flag) comm_write_step(p.comm, step + 1u);
-        }
-        named_barrier(1, kRingConsumerThreads);
-        if (!s_flag) return;
+        // the same thread collects the ranks' shares of its elements, in rank order
         for (int idx = tid; idx < p.ntok * kRingTileRows; idx += kRingConsumerThreads) {
             const int b = idx >> 4, j = idx & (kRingTileRows - 1);
             if (j >= hr) continue;
             const size_t o = (size_t)b * p.H + h0 + j;
-            float v = comm_sum(p.comm, parity, o);
+            float v;
+            if (!comm_get_sum(p.comm, p.ctl, step, o, &v)) continue;
             if (p.add_residual) v += to_float<T>(x[o]);
             out[o] = from_float<T>(v);
         }
+        // every CTA read the counter at entry, before the first grid barrier
+        if (cta == 0 && tid == 0) comm_write_step(p.comm, step + 1u);
     }
     if (tracer) trace_stamp(p.ctl, 9);
 }
