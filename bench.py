@@ -20,8 +20,8 @@ reports the achieved HBM bandwidth (algorithmic bytes / step time) against the m
                  32K-context attention, linear attention), same method, reported for context.
 
 With N > 1 (torchrun, one rank per GPU) the MoE runs expert-parallel: every rank holds 256/N
-experts and 1/N of the shared expert, and one NCCL all-reduce of the fp32 partial closes the step
-(strong scaling: the total work is fixed).
+experts and 1/N of the shared expert, and the kernels sum the ranks' fp32 partial outputs over
+peer memory in their epilogue (strong scaling: the total work is fixed).
 """
 
 from __future__ import annotations
@@ -138,6 +138,15 @@ def time_graph(step_fns, warmup: int, min_region_s: float = 0.0):
         return start.elapsed_time(end), graph, stream
 
 
+def hold_load(graph, stream, replays: int):
+    """Replays a captured graph `replays` more times (untimed) so that the clock sampler, which
+    cannot sample faster than every 100 ms, sees the same load as the few-millisecond timed replay."""
+    with torch.cuda.stream(stream):
+        for _ in range(replays):
+            graph.replay()
+        stream.synchronize()
+
+
 def build_moe_sets(device, n_sets: int, seed: int = 0):
     import mega_kernel_qwen36 as mk
     from mega_kernel_qwen36 import synthetic as syn
@@ -154,7 +163,7 @@ def distinct_experts(indices: torch.Tensor) -> int:
     return int(torch.unique(indices).numel())
 
 
-def bench_moe(device, batch: int, steps: int, warmup: int, sets, host_weights, peak):
+def bench_moe(device, batch: int, steps: int, warmup: int, sets, host_weights, peak, hold_s: float = 0.0):
     """Graph-timed MoE steps rotating over the weight sets and over different tokens."""
     import mega_kernel_qwen36 as mk
     from mega_kernel_qwen36 import synthetic as syn
@@ -168,6 +177,8 @@ def bench_moe(device, batch: int, steps: int, warmup: int, sets, host_weights, p
         uniq.append(distinct_experts(idx))
     fns = [(lambda i=i: mk.moe_decode(xs[i % n_tokens], sets[i % len(sets)], top_k=8, backend="persistent")) for i in range(steps)]
     ms, graph, stream = time_graph(fns, warmup)
+    if hold_s > 0:
+        hold_load(graph, stream, max(1, int(hold_s * 1e3 / max(ms, 1e-3))))
     bytes_per_step = statistics.mean(syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, batch, uniq[i % n_tokens]) for i in range(steps))
     us = ms * 1e3 / steps
     gbs = bytes_per_step / (us * 1e-6) / 1e9
@@ -364,10 +375,10 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     torch.cuda.synchronize()
-    res = bench_moe(device, ns.batch, ns.steps, ns.warmup, sets, host_weights, peak)
-    e2e = bench_e2e(device, ns.batch, ns.steps, ns.warmup, sets)
-    time.sleep(0.25)
+    res = bench_moe(device, ns.batch, ns.steps, ns.warmup, sets, host_weights, peak, hold_s=0.8)
     clocks = sampler.stop()
+    clocks["sampled_over"] = "the timed graph replay and 0.8 s of further replays of the same graph"
+    e2e = bench_e2e(device, ns.batch, ns.steps, ns.warmup, sets)
 
     others = {}
     if not ns.no_others:
@@ -399,8 +410,45 @@ def main():
     print(json.dumps(line), flush=True)
 
 
+def bench_dense_tp(ns, world, rank, device, exchange, peak):
+    """Tensor-parallel dense FFN (27B shape) on the same ranks: one kernel per step per GPU with the
+    cross-GPU sum inside, graph-timed like the headline.  Collective: every rank calls it."""
+    import torch.distributed as dist
+
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import parallel, synthetic as syn
+
+    out = {}
+    host = syn.dense_weights(syn.DENSE_27B, 0)
+    cut = parallel.shard_dense_weights(mk.DenseFfnWeights(*[host[f] for f in syn.DENSE_WEIGHT_FIELDS]), rank, world)
+    local = mk.DenseFfnWeights(*[getattr(cut, f).to(device) for f in syn.DENSE_WEIGHT_FIELDS])
+    copies = [local]
+    per_rank = syn.dense_algorithmic_bytes(syn.DENSE_27B, 1) // world
+    while per_rank * len(copies) < 3 * L2_BYTES:  # rotate so that the working set exceeds the L2
+        copies.append(mk.DenseFfnWeights(*[getattr(local, f).clone() for f in syn.DENSE_WEIGHT_FIELDS]))
+    del host, cut
+    n = max(len(copies), min(ns.steps, 40))
+    for batch in (1, 8):
+        x = syn.hidden_states(batch, syn.DENSE_27B.hidden, seed=7).to(device)
+        mk.ops._C.dense_ffn_decode_partial(x, *[getattr(local, f) for f in syn.DENSE_WEIGHT_FIELDS], 1e-6)  # local warm-up
+        torch.cuda.synchronize()
+        dist.barrier()
+        fns = [(lambda i=i: parallel.dense_ffn_decode_tp(x, copies[i % len(copies)], exchange=exchange)) for i in range(n)]
+        ms, _, _ = time_graph(fns, 3)
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t) * 1e3 / n
+        nbytes = syn.dense_algorithmic_bytes(syn.DENSE_27B, batch)
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[f"dense_ffn_27b_tp{world}_b{batch}"] = {"us_per_step": round(us, 3), "bytes_per_step": nbytes, "achieved_gbs": round(gbs, 1),
+                                                   "frac_of_measured": round(gbs / (peak * world), 4)}
+        dist.barrier()
+    return out
+
+
 def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
-    """N ranks, one per GPU: expert-parallel MoE step = local kernel + NCCL all-reduce + residual."""
+    """N ranks, one per GPU: expert-parallel MoE step, the ranks' partial outputs summed inside the
+    kernel over peer memory (or, with --collective nccl, by an all-reduce after it)."""
     import torch.distributed as dist
 
     import mega_kernel_qwen36 as mk
@@ -431,6 +479,12 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
     def step(i):
         return parallel.moe_decode_ep(xs[i % n_tokens], shards[i % len(shards)], top_k=8, exchange=exchange)
 
+    # distinct experts per token set (identical on all ranks), for the algorithmic byte count
+    uniq = []
+    for i in range(n_tokens):
+        _, idx, _ = step(i)
+        uniq.append(distinct_experts(idx))
+
     sampler = ClockSampler(device.index)
     if rank == 0:
         sampler.start()
@@ -449,6 +503,10 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
             end.record(stream)
             end.synchronize()
         ms = torch.tensor([start.elapsed_time(end)], device=device)
+        # the same number of further replays on every rank, for the clock sampler
+        worst = ms.clone()
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        hold_load(graph, stream, max(1, int(800.0 / max(float(worst), 1e-3))))
         timing = "CUDA graph of all steps (one kernel per step per GPU, cross-GPU sum inside the kernel), CUDA events, max over ranks"
     else:
         for i in range(ns.warmup):
@@ -466,6 +524,7 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
         timing = "eager launches (kernel + NCCL all-reduce + residual per step), CUDA events, max over ranks"
     dist.barrier()
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
     e2e = None
     host_x = [x.cpu().pin_memory() for x in xs]
     host_out = torch.empty_like(host_x[0]).pin_memory()
@@ -483,10 +542,12 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
     dist.all_reduce(dt, op=dist.ReduceOp.MAX)
     nbytes = ns.batch * syn.MOE_35B_A3B.hidden * 2
     e2e = {"value": round(float(dt) / ns.steps * 1e6, 3), "unit": "us", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+    others = {}
+    if not ns.no_others and exchange is not None:
+        others = bench_dense_tp(ns, world, rank, device, exchange, peak)
     if rank == 0:
-        clocks = sampler.stop()
         us = float(ms) * 1e3 / ns.steps
-        nbytes_alg = syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, ns.batch, min(8 * ns.batch, 256))
+        nbytes_alg = statistics.mean(syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, ns.batch, uniq[i % n_tokens]) for i in range(ns.steps))
         gbs = nbytes_alg / (us * 1e-6) / 1e9
         line = {
             "metric": "us_per_decode_step", "value": round(us, 3), "unit": "us", "n_gpus": world, "steps": ns.steps,
@@ -496,7 +557,7 @@ def run_expert_parallel(ns, world, rank, device, peak, peak_kind):
                          "frac": round(gbs / (peak * world), 4), "peak_kind": f"of {peak_kind} x {world} GPUs",
                          "algorithmic_bytes_per_launch": nbytes_alg, "traffic": None},
             "cpu_baseline": None, "e2e": e2e, "gpu_launches": ns.steps, "clocks": clocks,
-            "timing": timing,
+            "timing": timing, "others": others,
         }
         print(json.dumps(line), flush=True)
     torch.cuda.synchronize()
