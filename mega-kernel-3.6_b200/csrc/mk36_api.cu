@@ -127,6 +127,10 @@ int mk36_set_option(const char* name, int value) {
         options().force_generic = value ? 1 : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "ring_mma") == 0) {
+        options().ring_mma = value ? 1 : 0;
+        return MK36_OK;
+    }
     MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
 }
 

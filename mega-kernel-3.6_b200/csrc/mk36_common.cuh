@@ -73,6 +73,7 @@ inline FastDiv make_fastdiv(unsigned d) {
 // Process-wide switches set through mk36_set_option (tests use them to reach every code path).
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
+    int ring_mma = 0;       // 1: the MoE ring kernel contracts with mma.sync whatever the token count
 };
 Options& options();
 

@@ -43,6 +43,7 @@ constexpr int kRingGroups = 3;
 constexpr int kRingGroupWarps = kRingConsumerWarps / kRingGroups;
 constexpr int kRingGroupThreads = kRingGroupWarps * 32;
 constexpr int kRingMaxStages = 6;   // kRingGroups x (1 or 2)
+constexpr int kRingMaxDed = 4;      // single-use slots for the first down-projection chunks
 constexpr int kRingMaxTokens = 8;   // = N of the MMA tile
 constexpr int kRingMaxPairs = 64;
 constexpr int kRingTileRows = 16;   // = M of the MMA tile
@@ -71,13 +72,15 @@ struct MoeRingParams {
     int expert_base, local_experts, add_residual;
     float eps;
     int nstages;
+    int nded;     // shared memory left over by the ring, in stage-sized single-use slots (see off_ded)
     int rows_h;   // rows of length H per stage (<= 16, even; pairs per stage = rows_h / 2)
     int epc;      // experts per stage in the down phase (<= 4)
     int hr_max;   // max output rows per CTA (<= 16)
+    int scalar;   // 1: at most two tokens in the launch, contract with plain FMAs instead of mma.sync
     int log2_depth;   // stages per consumer group = 1 << log2_depth; nstages = kRingGroups << log2_depth
-    FastDiv fd_ncta, fd_rows_h, fd_pr, fd_I, fd_K, fd_qi, fd_qis, fd_epc;
+    FastDiv fd_ncta, fd_rows_h, fd_pr, fd_I, fd_K, fd_qi, fd_qis, fd_epc, fd_ks;
     // byte offsets into dynamic shared memory
-    int off_ring, off_sdown, off_act, off_part, off_red, off_logits, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
+    int off_ded, off_ring, off_sdown, off_act, off_part, off_red, off_logits, off_uniq_e, off_uniq_m, off_pair_e, off_pair_w, off_bars;
     CommParams comm;  // world > 1: the epilogue sums the ranks' partial outputs over peer memory
 };
 
@@ -220,6 +223,117 @@ __device__ __noinline__ void tile_times_split_vectors(float (&d)[4], const T* ba
     add4(d, e[0]);
 }
 
+// ---- plain-FMA contraction for launches of one or two tokens ----
+// On this part a warp-level mma.sync costs tens of issue cycles, so for a handful of token columns
+// unpack + FMA needs several times fewer cycles than the tensor-core instruction that computes
+// eight columns at once.  A warp takes whole rows (no partial tiles to combine, hence no barrier
+// between the warps of a group): lane l reads the 16-byte pieces l, l + 32, ... of the row, which
+// is conflict-free in shared memory, and the warp reduces with shuffles.
+
+// Dot products of row `ra` (and, when PAIR, row `rb`) of `nchunks` 8-element pieces with NT vectors of T.
+template <typename T, int NT, bool PAIR>
+__device__ __forceinline__ void dot_rows_t(const T* ra, const T* rb, const T* const (&xp)[NT], int nchunks, int lane, float (&sa)[NT],
+                                           float (&sb)[NT]) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { sa[t] = 0.0f; sb[t] = 0.0f; }
+#pragma unroll 2
+    for (int c = lane; c < nchunks; c += 32) {
+        float fa[8], fb[8];
+        unpack_u4<T>(lds128(ra + 8 * c), fa);
+        if (PAIR) unpack_u4<T>(lds128(rb + 8 * c), fb);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float fx[8];
+            unpack_u4<T>(lds128(xp[t] + 8 * c), fx);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                sa[t] = fmaf(fa[i], fx[i], sa[t]);
+                if (PAIR) sb[t] = fmaf(fb[i], fx[i], sb[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        sa[t] = warp_sum(sa[t]);
+        if (PAIR) sb[t] = warp_sum(sb[t]);
+    }
+}
+
+// One (gate, up) pair or one single row against one or two token vectors; results in ga[j] / ua[j]
+// (ua only when rb is given).
+template <typename T>
+__device__ __forceinline__ void rows_times_tokens(const T* ra, const T* rb, const T* x0, const T* x1, const T* x2, const T* x3, int nvec,
+                                               int nchunks, int lane, float (&ga)[4], float (&ua)[4]) {
+    if (nvec <= 1) {
+        const T* const xp[1] = {x0};
+        float a[1], b[1];
+        if (rb) dot_rows_t<T, 1, true>(ra, rb, xp, nchunks, lane, a, b);
+        else dot_rows_t<T, 1, false>(ra, rb, xp, nchunks, lane, a, b);
+        ga[0] = a[0]; ua[0] = b[0];
+    } else {  // the plain-FMA path is only taken for launches of one or two tokens
+        const T* const xp[2] = {x0, x1};
+        float a[2], b[2];
+        if (rb) dot_rows_t<T, 2, true>(ra, rb, xp, nchunks, lane, a, b);
+        else dot_rows_t<T, 2, false>(ra, rb, xp, nchunks, lane, a, b);
+        ga[0] = a[0]; ga[1] = a[1]; ua[0] = b[0]; ua[1] = b[1];
+    }
+}
+
+// Down projection, plain-FMA path: four lanes share a row (lane t of the four takes the 16-byte pieces
+// t, t + 4, ...), so a warp works on eight rows at once and one pass of a group's four warps covers a
+// whole chunk; many independent rows in flight instead of one latency chain per row.  The
+// activations are fp32 in shared memory; lanes on different rows read the same activation
+// address (a broadcast).  Returns the quad-reduced sums in every lane of the quad.
+template <typename T, int NT>
+__device__ __forceinline__ void quad_row_dot(const T* row, const float* const (&ap)[NT], int nchunks, int t4, float (&s)[NT]) {
+    float s2[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { s[t] = 0.0f; s2[t] = 0.0f; }
+    int c = t4;
+    for (; c + 4 < nchunks; c += 8) {
+        float f[8], g[8];
+        unpack_u4<T>(lds128(row + 8 * c), f);
+        unpack_u4<T>(lds128(row + 8 * (c + 4)), g);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float4 a = *reinterpret_cast<const float4*>(ap[t] + 8 * c);
+            const float4 b = *reinterpret_cast<const float4*>(ap[t] + 8 * c + 4);
+            const float4 a2 = *reinterpret_cast<const float4*>(ap[t] + 8 * (c + 4));
+            const float4 b2 = *reinterpret_cast<const float4*>(ap[t] + 8 * (c + 4) + 4);
+            float v = s[t], w = s2[t];
+            v = fmaf(f[0], a.x, v); w = fmaf(g[0], a2.x, w);
+            v = fmaf(f[1], a.y, v); w = fmaf(g[1], a2.y, w);
+            v = fmaf(f[2], a.z, v); w = fmaf(g[2], a2.z, w);
+            v = fmaf(f[3], a.w, v); w = fmaf(g[3], a2.w, w);
+            v = fmaf(f[4], b.x, v); w = fmaf(g[4], b2.x, w);
+            v = fmaf(f[5], b.y, v); w = fmaf(g[5], b2.y, w);
+            v = fmaf(f[6], b.z, v); w = fmaf(g[6], b2.z, w);
+            v = fmaf(f[7], b.w, v); w = fmaf(g[7], b2.w, w);
+            s[t] = v; s2[t] = w;
+        }
+    }
+    for (; c < nchunks; c += 4) {
+        float f[8];
+        unpack_u4<T>(lds128(row + 8 * c), f);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float4 a = *reinterpret_cast<const float4*>(ap[t] + 8 * c);
+            const float4 b = *reinterpret_cast<const float4*>(ap[t] + 8 * c + 4);
+            float v = s[t];
+            v = fmaf(f[0], a.x, v); v = fmaf(f[1], a.y, v); v = fmaf(f[2], a.z, v); v = fmaf(f[3], a.w, v);
+            v = fmaf(f[4], b.x, v); v = fmaf(f[5], b.y, v); v = fmaf(f[6], b.z, v); v = fmaf(f[7], b.w, v);
+            s[t] = v;
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        float v = s[t] + s2[t];
+        v += __shfl_xor_sync(kFullMask, v, 1);
+        v += __shfl_xor_sync(kFullMask, v, 2);
+        s[t] = v;
+    }
+}
+
 // position of the q-th set bit of m (q < popcount(m))
 __device__ __forceinline__ int nth_set_bit(unsigned long long m, int q) {
     for (int i = 0; i < q; ++i) m &= m - 1;
@@ -256,6 +370,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + p.off_bars);
     unsigned long long* empty_bar = full_bar + kRingMaxStages;
     unsigned long long* sdown_bar = empty_bar + kRingMaxStages;
+    unsigned long long* ded_bar = sdown_bar + 1;
+    unsigned char* ded = smem + p.off_ded;
 
     const T* x = static_cast<const T*>(p.x);
     const int NS = p.nstages;
@@ -292,6 +408,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             mbar_init(&empty_bar[s], kRingGroupWarps);
         }
         mbar_init(sdown_bar, 1);
+        for (int s = 0; s < kRingMaxDed; ++s) mbar_init(&ded_bar[s], 1);
         mbar_init_fence();
     }
     __syncthreads();
@@ -344,7 +461,28 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             const int nB = chunks_in(t0, t1, p.fd_pr);
             const int mB = fdiv(t0, p.fd_pr);
             const int nC = (hr > 0) ? fdiv(n_unique + p.epc - 1, p.fd_epc) : 0;
+            const int nd = min(p.nded, nC);  // down chunks that get a slot of their own
+            const unsigned cbytes = (unsigned)((size_t)hr * p.I * sizeof(T));
+            auto issue_down = [&](int k, unsigned char* dst, unsigned long long* bar) {
+                const int ua = k * p.epc, ub = min(n_unique, ua + p.epc);
+                for (int u = ua; u < ub; ++u) {
+                    const int e = s_uniq_e[u] - p.expert_base;
+                    bulk_copy_g2s(dst + (size_t)(u - ua) * p.hr_max * p.I * sizeof(T),
+                                  static_cast<const T*>(p.edown) + ((size_t)e * p.H + h0) * p.I, cbytes, bar);
+                }
+            };
+            auto down_bytes = [&](int k) { return cbytes * (unsigned)(min(n_unique, (k + 1) * p.epc) - k * p.epc); };
             for (int k = 0; k < nB && ok; ++k) {
+                if (k == NS || (k == nB - 1 && nB <= NS)) {
+                    // The ring is full of gate/up rows (or they are all requested): now ask for the down rows
+                    // that have a slot of their own.  They are not needed before the second grid barrier, and
+                    // requesting them here keeps them out of the way of the first gate/up rows.
+                    if (cta == 0) trace_stamp(p.ctl, 17);
+                    for (int c = 0; c < nd; ++c) {
+                        mbar_arrive_expect_tx(&ded_bar[c], down_bytes(c));
+                        issue_down(c, ded + (size_t)c * kRingStageBytes, &ded_bar[c]);
+                    }
+                }
                 int first, count, u, i;
                 chunk_span(t0, t1, PR, mB, k, first, count);
                 fdivmod(first, p.fd_I, u, i);
@@ -360,20 +498,17 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
                     bulk_copy_g2s(dst + up_off * sizeof(T), static_cast<const T*>(p.eup) + off, bytes, &full_bar[stage_of(n)]);
                 }
             }
-            const unsigned cbytes = (unsigned)((size_t)hr * p.I * sizeof(T));
-            for (int k = 0; k < nC && ok; ++k) {
-                const int ua = k * p.epc, ub = min(n_unique, ua + p.epc);
-                const int n = nA + nB + k;
-                unsigned char* dst = acquire(n, cbytes * (unsigned)(ub - ua));
-                if (cta == 0 && k == 0) trace_stamp(p.ctl, 17);
-                if (cta == 0 && k == nC - 1) trace_stamp(p.ctl, 18);
-                if (dst) {
-                    for (int u = ua; u < ub; ++u) {
-                        const int e = s_uniq_e[u] - p.expert_base;
-                        bulk_copy_g2s(dst + (size_t)(u - ua) * p.hr_max * p.I * sizeof(T),
-                                      static_cast<const T*>(p.edown) + ((size_t)e * p.H + h0) * p.I, cbytes, &full_bar[stage_of(n)]);
-                    }
+            if (nB == 0) {
+                for (int c = 0; c < nd; ++c) {
+                    mbar_arrive_expect_tx(&ded_bar[c], down_bytes(c));
+                    issue_down(c, ded + (size_t)c * kRingStageBytes, &ded_bar[c]);
                 }
+            }
+            for (int k = nd; k < nC && ok; ++k) {
+                const int n = nA + nB + (k - nd);
+                unsigned char* dst = acquire(n, down_bytes(k));
+                if (cta == 0 && k == nC - 1) trace_stamp(p.ctl, 18);
+                if (dst) issue_down(k, dst, &full_bar[stage_of(n)]);
             }
         }
         if (lane == 0 && !ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingProducer);
@@ -454,6 +589,58 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         bool got = ok;
         if (got) got = mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
         if (!got) ok = false;
+        if (p.scalar) {
+            // a warp takes whole rows (router) or whole (gate, up) pairs: nothing to combine across warps
+            if (got) {
+                const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
+                const int nch = p.H >> 3;
+                for (int r = wi; r < count; r += kRingGroupWarps) {
+                    float ga[4], ua[4];
+                    if (kind == 0) {
+                        rows_times_tokens<T>(sbase + (size_t)r * rowH, nullptr, xs, xs + rowH, xs + 2 * rowH, xs + 3 * rowH, p.ntok, nch, lane,
+                                             ga, ua);
+                        if (lane == 0) {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (t < p.ntok) p.logits[(size_t)t * p.E + first + r] = ga[t];
+                        }
+                    } else {
+                        int slot[4] = {0, 0, 0, 0};
+                        int nvec = p.ntok;
+                        if (kind == 1) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) slot[j] = (j < p.ntok) ? j : 0;
+                        } else {
+                            nvec = __popcll(mask);
+                            unsigned long long m = mask;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (m) { slot[j] = __ffsll((long long)m) - 1; m &= m - 1; }
+                                else slot[j] = slot[0];
+                            }
+                        }
+                        const T* xv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) xv[j] = xs + (size_t)((kind == 1) ? slot[j] : fdiv(slot[j], p.fd_K)) * rowH;
+                        rows_times_tokens<T>(sbase + (size_t)r * rowH, sbase + (size_t)(PR + r) * rowH, xv[0], xv[1], xv[2], xv[3], nvec, nch,
+                                             lane, ga, ua);
+                        if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (j < nvec) {
+                                    const float a = silu(ga[j]) * ua[j];
+                                    if (kind == 1) p.sact[(size_t)slot[j] * p.Is + first + r] = a;
+                                    else p.act[(size_t)slot[j] * p.I + i0 + r] = a;
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[stage]);  // the stage has been read
+            }
+            return;
+        }
         float* mine = gred + ((size_t)gbuf * kRingGroupWarps + wi) * 128;
         if (got) {
             const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
@@ -696,6 +883,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     const int npairs = p.ntok * p.K;
     const size_t act_elems = (size_t)npairs * p.I + (size_t)p.ntok * p.Is;
     T* acts_lo = acts_hi + act_elems;
+    float* actf = reinterpret_cast<float*>(smem + p.off_act);  // plain-FMA path: the activations stay fp32
     const size_t shared_base = (size_t)npairs * p.I;  // element offset of the shared expert's activations
     const int nC_all = (hr > 0) ? fdiv(n_unique + p.epc - 1, p.fd_epc) : 0;
     if (ok) {
@@ -734,6 +922,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             for (int q = 0; q < kActBatch; ++q) {
                 if (dst[q] >= 0) {
                     const float in[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+                    if (p.scalar) {
+                        *reinterpret_cast<float4*>(actf + dst[q]) = v[q];
+                        continue;
+                    }
                     T hi[4], lo[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -752,6 +944,76 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     // ---- phase C: down rows.  part[slot][row]: slot < npairs routed pairs, then one per token (shared).
     //      One warp contracts one expert's block of rows over the whole intermediate length. ----
     const int nC = nC_all;
+    if (p.scalar) {
+        // at most two tokens in the launch (see the host side): a row meets at most two activation vectors
+        const int nchI = p.I >> 3, nchIs = p.Is >> 3;
+        const int ndc = min(p.nded, nC);
+        const int rg = lane >> 2, t4 = lane & 3;
+        // shared expert's rows: the last group, which owns the fewest routed chunks
+        if (group == kRingGroups - 1 && hr > 0 && p.Is > 0) {
+            bool got = ok;
+            if (got) got = mbar_wait(sdown_bar, 0, &s_abort);
+            if (!got) ok = false;
+            if (got) {
+                const float* const ap[2] = {actf + shared_base, actf + shared_base + (p.ntok > 1 ? p.Is : 0)};
+                for (int r0w = 0; r0w < hr; r0w += 8 * kRingGroupWarps) {
+                    const int row = r0w + wi * 8 + rg;
+                    const bool live = row < hr;
+                    float sv[2];
+                    quad_row_dot<T, 2>(sdown_buf + (size_t)(live ? row : 0) * p.Is, ap, nchIs, t4, sv);
+                    if (live && t4 == 0) {
+                        part[(npairs + 0) * p.hr_max + row] = sv[0];
+                        if (p.ntok > 1) part[(npairs + 1) * p.hr_max + row] = sv[1];
+                    }
+                }
+            }
+        }
+        if (tracer) trace_stamp(p.ctl, 12);
+        for (int k = 0; k < nC; ++k) {
+            const bool own_slot = k < ndc;
+            const int n = nA + nB + (k - ndc);
+            if ((own_slot ? k : n) % kRingGroups != group) continue;
+            const int stage = own_slot ? 0 : stage_of(n);
+            const unsigned char* slot = own_slot ? ded + (size_t)k * kRingStageBytes : ring + (size_t)stage * kRingStageBytes;
+            bool got = ok;
+            if (got) got = own_slot ? mbar_wait(&ded_bar[k], 0, &s_abort) : mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
+            if (!got) { ok = false; continue; }
+            const bool first_chunk = tracer && k == group;
+            if (first_chunk) trace_stamp(p.ctl, 13);
+            if (tracer && !first_chunk) trace_stamp(p.ctl, 19);
+            const int nexp = min(p.epc, n_unique - k * p.epc);
+            const int ntasks = nexp * hr;  // (expert slot, row) pairs of this chunk
+            for (int t0w = 0; t0w < ntasks; t0w += 8 * kRingGroupWarps) {
+                const int task = t0w + wi * 8 + rg;
+                const bool live = task < ntasks;
+                const int tk = live ? task : 0;
+                const int es = (tk >= hr) + (tk >= 2 * hr) + (tk >= 3 * hr);
+                const int row = tk - es * hr;
+                const unsigned long long m = s_uniq_m[k * p.epc + es];
+                const int p0 = __ffsll((long long)m) - 1;
+                const unsigned long long m1 = m & (m - 1);
+                const int p1 = m1 ? (__ffsll((long long)m1) - 1) : p0;
+                const float* const ap[2] = {actf + (size_t)p0 * p.I, actf + (size_t)p1 * p.I};
+                const T* wrow = reinterpret_cast<const T*>(slot) + ((size_t)es * p.hr_max + row) * p.I;
+                float sv[2];
+                if (p.ntok > 1) {
+                    quad_row_dot<T, 2>(wrow, ap, nchI, t4, sv);
+                } else {
+                    const float* const a1[1] = {ap[0]};
+                    float s1[1];
+                    quad_row_dot<T, 1>(wrow, a1, nchI, t4, s1);
+                    sv[0] = s1[0]; sv[1] = 0.0f;
+                }
+                if (live && t4 == 0) {
+                    part[p0 * p.hr_max + row] = sv[0];
+                    if (m1) part[p1 * p.hr_max + row] = sv[1];
+                }
+            }
+            if (first_chunk) trace_stamp(p.ctl, 20);
+            __syncwarp();
+            if (lane == 0 && !own_slot) mbar_arrive(&empty_bar[stage]);  // the stage has been read
+        }
+    } else {
     if (warp == kRingConsumerWarps - 1 && hr > 0 && p.Is > 0) {
         // shared expert: rows from the dedicated buffer, columns = tokens
         bool got = ok;
@@ -770,42 +1032,75 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         }
     }
     if (tracer) trace_stamp(p.ctl, 12);
+    const int nd = min(p.nded, nC);
+    // The warps of a group share a chunk: warp wi takes expert slot wi % epc and part wi / epc of the
+    // intermediate length (mma.sync is slow enough that one warp per expert would make this phase
+    // compute-bound); the parts meet in shared memory at the group's barrier.
+    const int ks = kRingGroupWarps / p.epc;           // parts of the contraction (epc is 1, 2 or 4)
+    const int eslot = wi & (p.epc - 1);
+    const int kpart = wi >> ((p.epc == 4) ? 2 : (p.epc == 2 ? 1 : 0));
+    const int klen = fdiv(p.I, p.fd_ks);               // multiple of 32 (checked by the host)
     for (int k = 0; k < nC; ++k) {
-        const int n = nA + nB + k;
-        if (n % kRingGroups != group) continue;
-        const int stage = stage_of(n);
+        // the first nd chunks sit in slots of their own (requested during the gate/up stream), the rest
+        // come through the ring
+        const bool own_slot = k < nd;
+        const int n = nA + nB + (k - nd);
+        if ((own_slot ? k : n) % kRingGroups != group) continue;
+        const int stage = own_slot ? 0 : stage_of(n);
+        const unsigned char* slot = own_slot ? ded + (size_t)k * kRingStageBytes : ring + (size_t)stage * kRingStageBytes;
         bool got = ok;
-        if (got) got = mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
-        if (!got) { ok = false; continue; }
-        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 13);
-        if (tracer && k >= kRingGroups) trace_stamp(p.ctl, 19);
-        const int u = k * p.epc + wi;
-        if (wi < p.epc && u < n_unique) {
-            const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes) + (size_t)wi * p.hr_max * p.I;
-            const unsigned long long mask = s_uniq_m[u];
+        if (got) got = own_slot ? mbar_wait(&ded_bar[k], 0, &s_abort) : mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
+        if (!got) ok = false;
+        const bool first_chunk = tracer && k == group;  // diagnostic stamps of the tracer's first chunk
+        if (first_chunk) trace_stamp(p.ctl, 13);
+        if (tracer && !first_chunk) trace_stamp(p.ctl, 19);
+        const int u = k * p.epc + eslot;
+        const bool work = got && u < n_unique;
+        unsigned long long mask = 0ull;
+        float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (work) {
+            const T* sbase = reinterpret_cast<const T*>(slot) + (size_t)eslot * p.hr_max * p.I + (size_t)kpart * klen;
+            mask = s_uniq_m[u];
             const int ncol = __popcll(mask);
             const T* ch = nullptr;
             const T* cl = nullptr;
             if (fg < ncol) {
                 const int pair = nth_set_bit(mask, fg);
-                ch = acts_hi + (size_t)pair * p.I;
-                cl = acts_lo + (size_t)pair * p.I;
+                ch = acts_hi + (size_t)pair * p.I + (size_t)kpart * klen;
+                cl = acts_lo + (size_t)pair * p.I + (size_t)kpart * klen;
             }
-            float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (tracer && k < kRingGroups) trace_stamp(p.ctl, 20);
-            tile_times_split_vectors<T>(d, sbase, p.I, hr, ch, cl, p.I, lane);
-            if (tracer && k < kRingGroups) trace_stamp(p.ctl, 21);
+            tile_times_split_vectors<T>(d, sbase, p.I, hr, ch, cl, klen, lane);
+        }
+        if (first_chunk) trace_stamp(p.ctl, 20);
+        __syncwarp();
+        if (lane == 0 && !own_slot && got) mbar_arrive(&empty_bar[stage]);  // the stage has been read
+        float* mine = gred + ((size_t)gbuf * kRingGroupWarps + wi) * 128;
+        if (ks > 1) {
+            if (work && kpart > 0) {
+                *reinterpret_cast<float2*>(mine + fg * 8 + 2 * ft) = make_float2(d[0], d[1]);
+                *reinterpret_cast<float2*>(mine + (fg + 8) * 8 + 2 * ft) = make_float2(d[2], d[3]);
+            }
+            named_barrier(2 + group, kRingGroupThreads);  // every warp of the group walks through, whatever happened
+        }
+        if (first_chunk) trace_stamp(p.ctl, 21);
+        if (work && kpart == 0) {
+            const int ncol = __popcll(mask);
+            for (int part_i = 1; part_i < ks; ++part_i) {
+                const float* other = gred + ((size_t)gbuf * kRingGroupWarps + eslot + part_i * p.epc) * 128;
+                const float2 lo2 = *reinterpret_cast<const float2*>(other + fg * 8 + 2 * ft);
+                const float2 hi2 = *reinterpret_cast<const float2*>(other + (fg + 8) * 8 + 2 * ft);
+                d[0] += lo2.x; d[1] += lo2.y; d[2] += hi2.x; d[3] += hi2.y;
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int row = fg + ((q & 2) ? 8 : 0), col = 2 * ft + (q & 1);
                 if (row < hr && col < ncol) part[nth_set_bit(mask, col) * p.hr_max + row] = d[q];
             }
         }
-        __syncwarp();
-        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 22);
-        if (lane == 0) mbar_arrive(&empty_bar[stage]);
-        if (tracer && k < kRingGroups) trace_stamp(p.ctl, 23);
+        if (first_chunk) trace_stamp(p.ctl, 22);
+        gbuf ^= 1;
     }
+    }  // tensor-core path
     if (tracer) trace_stamp(p.ctl, 14);
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
     named_barrier(1, kRingConsumerThreads);
@@ -886,6 +1181,8 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
         return MK36_OK;  // the kernel's index arithmetic is 31-bit
     int epc = (int)(kRingStageBytes / down_block);
     if (epc > kRingGroupWarps) epc = kRingGroupWarps;
+    if (epc == 3) epc = 2;  // the group's warps split into epc expert slots x (4 / epc) parts of the contraction
+    if (I % (32 * (kRingGroupWarps / epc)) != 0) return MK36_OK;
 
     int tb = kRingMaxTokens;
     while (tb > 1 && (long long)tb * K > kRingMaxPairs) tb >>= 1;
@@ -907,7 +1204,7 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
         off += bytes;
         return (int)at;
     };
-    int nstages = 0;
+    int nstages = 0, nded = 0;
     for (; tb >= 1; tb >>= 1) {
         off = 0;
         const int pairs = tb * K;
@@ -922,16 +1219,22 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
         p.off_uniq_m = take(kRingMaxPairs * 8, 16);
         p.off_pair_e = take(kRingMaxPairs * 4, 16);
         p.off_pair_w = take(kRingMaxPairs * 4, 16);
-        p.off_bars = take((2 * kRingMaxStages + 1) * 8, 16);
+        p.off_bars = take((2 * kRingMaxStages + 1 + kRingMaxDed) * 8, 16);
         p.off_ring = take(0, 128);
         const long long room = (long long)dev->max_smem_optin - (long long)off - 1024;
         nstages = (int)(room / kRingStageBytes);
-        // every consumer group owns one or two stages of its own (see stage_of below)
+        // every consumer group owns one or two stages of its own (see stage_of below); what is left over
+        // becomes single-use slots for the first down-projection chunks
+        const int fit = nstages;
         nstages = (nstages >= 2 * kRingGroups) ? 2 * kRingGroups : (nstages >= kRingGroups ? kRingGroups : 0);
+        nded = fit - nstages;
+        if (nded > kRingMaxDed) nded = kRingMaxDed;
         if (nstages > 0) break;
     }
     if (tb < 1) return MK36_OK;
-    const size_t smem_bytes = (size_t)p.off_ring + (size_t)nstages * kRingStageBytes;
+    p.off_ded = p.off_ring + nstages * kRingStageBytes;
+    p.nded = nded;
+    const size_t smem_bytes = (size_t)p.off_ring + (size_t)(nstages + nded) * kRingStageBytes;
 
     const size_t scratch = align_up((size_t)tb * E * 4, 256) + align_up((size_t)tb * K * I * 4, 256) +
                            align_up((size_t)tb * (Is > 0 ? Is : 1) * 4, 256);
@@ -965,6 +1268,7 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
     p.epc = epc;
     p.hr_max = hr_max;
     p.log2_depth = (nstages >= 2 * kRingGroups) ? 1 : 0;
+    p.scalar = (tb <= 2 && !options().ring_mma) ? 1 : 0;
     p.fd_ncta = make_fastdiv(ncta);
     p.fd_rows_h = make_fastdiv(rows_h);
     p.fd_pr = make_fastdiv(pr);
@@ -973,6 +1277,7 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
     p.fd_qi = make_fastdiv(I / 4);
     p.fd_qis = make_fastdiv(Is > 0 ? Is / 4 : 1);
     p.fd_epc = make_fastdiv(epc);
+    p.fd_ks = make_fastdiv(kRingGroupWarps / epc);
 
     const void* kernel = (a->dtype == MK36_BF16) ? (const void*)moe_decode_ring_kernel<__nv_bfloat16>
                                                  : (const void*)moe_decode_ring_kernel<__half>;

@@ -74,6 +74,26 @@ def test_moe_general_kernel_matches_oracle(name, cuda_device):
     assert lib.mk36_set_option(b"no_such_option", 1) == cabi.MK36_ERR_INVALID_ARG
 
 
+@pytest.mark.parametrize("name", ["moe_small_bf16_b3", "moe_small_f16_b2", "moe_35b_bf16_b1_s0", "moe_35b_bf16_b8_s1"])
+def test_moe_ring_kernel_tensor_core_consumers_match_oracle(name, cuda_device):
+    """The ring kernel contracts with plain FMAs for launches of up to four tokens and with
+    mma.sync beyond; the switch forces the tensor-core consumers on the small launches as well."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    cabi.check(lib.mk36_set_option(b"ring_mma", 1))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(b"ring_mma", 0))
+    ref = run_oracle(case, spec)
+    assert_indices_exact(got["indices"], ref["indices"])
+    torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+    assert_output_parity(got["out"], ref["out"], what=name + " (tensor-core consumers)")
+
+
 @pytest.mark.parametrize("name", ["attn_27b_bf16_t1000", "attn_35b_bf16_t4096", "attn_35b_bf16_b2_t2500"])
 def test_attention_general_kernel_matches_oracle(name, cuda_device):
     """Shapes that normally take the tensor-core attention kernel, forced through the general one."""
