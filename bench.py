@@ -186,8 +186,9 @@ def bench_moe(device, batch: int, steps: int, warmup: int, sets, host_weights, p
             "frac_of_nominal_8tbs": gbs / NOMINAL_HBM_GBS, "distinct_experts_mean": statistics.mean(uniq)}
 
 
-def bench_others(device, steps: int, warmup: int, peak):
-    """Dense FFN, attention and linear attention at their measured shapes (rotating buffers)."""
+def bench_others(device, steps: int, warmup: int, peak, only=None):
+    """Dense FFN, attention and linear attention at their measured shapes (rotating buffers).
+    `only` ("dense", "attention" or "linear") restricts the run to one op, e.g. for a profiler."""
     import mega_kernel_qwen36 as mk
     from mega_kernel_qwen36 import synthetic as syn
 
@@ -200,10 +201,11 @@ def bench_others(device, steps: int, warmup: int, peak):
                      "frac_of_measured": round(gbs / peak, 4), "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
 
     # dense FFN 27B: 535 MB of weights per step already exceeds the L2
-    hw = syn.dense_weights(syn.DENSE_27B, 0)
-    dw = mk.DenseFfnWeights(*[hw[f].to(device) for f in syn.DENSE_WEIGHT_FIELDS])
+    want = lambda op: only in (None, op)
+    hw = syn.dense_weights(syn.DENSE_27B, 0) if want("dense") else None
+    dw = mk.DenseFfnWeights(*[hw[f].to(device) for f in syn.DENSE_WEIGHT_FIELDS]) if want("dense") else None
     n = max(4, min(steps, 20))
-    for batch in (1, 8):
+    for batch in ((1, 8) if want("dense") else ()):
         x = syn.hidden_states(batch, syn.DENSE_27B.hidden, seed=7).to(device)
         mk.dense_ffn_decode(x, dw)
         ms, _, _ = time_graph([lambda: mk.dense_ffn_decode(x, dw)] * n, min(warmup, 3))
@@ -212,7 +214,7 @@ def bench_others(device, steps: int, warmup: int, peak):
     torch.cuda.empty_cache()
 
     # attention: rotate over 4 caches (4 x 64 MiB > L2) at 32K; shorter contexts use more copies
-    for seq in (32768, 4096):
+    for seq in ((32768, 4096) if want("attention") else ()):
         copies = max(4, (3 * L2_BYTES) // (2 * seq * 2 * 256 * 2) + 1)
         t = syn.attention_tensors(1, 16, 2, 256, seq, seed=0)
         q = t["q"].to(device)
@@ -229,7 +231,7 @@ def bench_others(device, steps: int, warmup: int, peak):
         torch.cuda.empty_cache()
 
     # linear attention: rotate over states totalling > L2 (state is read and written: 2 x 2 MiB x B)
-    for batch in (1, 8):
+    for batch in ((1, 8) if want("linear") else ()):
         copies = (3 * L2_BYTES) // (batch * 32 * 128 * 128 * 4 * 2) + 2
         step = next(syn.linear_step_stream(batch, 16, 32, 128, 128, steps=1, seed=0))
         q, k, v = (step[n_].to(device) for n_ in ("q", "k", "v"))
@@ -343,6 +345,8 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="full weight sets to rotate over")
     ap.add_argument("--no-others", action="store_true", help="skip the context measurements of the other ops")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--others-only", choices=["dense", "attention", "linear"], default=None,
+                    help="run only that op's context measurement (for profiling one kernel on a small case)")
     ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
                     help="N > 1: sum the ranks' partials inside the kernel over peer memory, or with an NCCL all-reduce")
     ns = ap.parse_args()
@@ -369,6 +373,11 @@ def main():
 
     if world > 1:
         run_expert_parallel(ns, world, rank, device, peak, peak_kind)
+        return
+    if ns.others_only:
+        # one of the context ops alone (small enough to sit under a profiler); not a bench line
+        print(json.dumps({"others_only": ns.others_only, "steps": ns.steps,
+                          "others": bench_others(device, ns.steps, ns.warmup, peak, only=ns.others_only)}), flush=True)
         return
 
     host_weights, sets = build_moe_sets(device, ns.sets)

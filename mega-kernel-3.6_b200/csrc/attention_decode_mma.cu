@@ -300,7 +300,10 @@ int attention_decode_mma_launch(const mk36_attention_args* a, void* workspace, s
     const void* kernel = (a->dtype == MK36_BF16) ? mma_kernel_for<__nv_bfloat16>(D) : mma_kernel_for<__half>(D);
     if (!kernel) return MK36_OK;
     const size_t smem = (size_t)8 * D * 2 + ((size_t)kMmaAttnWarps * 8 * D + 2 * kMmaAttnWarps * 8) * 4;
-    MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+        const int rc_smem = ensure_dynamic_smem(kernel, smem);
+        if (rc_smem != MK36_OK) return rc_smem;
+    }
     const long long max_ctas = dev->sm_count;  // one CTA per SM (register budget)
     const long long per_batch = a->kv_heads;
     if (per_batch > max_ctas) return MK36_OK;

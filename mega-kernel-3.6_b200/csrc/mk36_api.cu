@@ -71,6 +71,27 @@ int launch_cooperative(const void* kernel, dim3 grid, dim3 block, size_t smem, c
     return MK36_OK;
 }
 
+// Raises the kernel's dynamic shared-memory limit when a launch needs more than was set before.
+// The setting is remembered per (device, kernel), so the driver call is made once, not per launch.
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    struct Entry { int device; const void* kernel; size_t bytes; };
+    static thread_local Entry cache[32];
+    static thread_local int used = 0;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    for (int i = 0; i < used; ++i) {
+        if (cache[i].device == dev && cache[i].kernel == kernel) {
+            if (cache[i].bytes >= bytes) return MK36_OK;
+            MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+            cache[i].bytes = bytes;
+            return MK36_OK;
+        }
+    }
+    MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (used < 32) cache[used++] = Entry{dev, kernel, bytes};
+    return MK36_OK;
+}
+
 int max_ctas_per_sm(const void* kernel, int threads, size_t smem) {
     int n = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem);

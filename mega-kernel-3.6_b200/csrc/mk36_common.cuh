@@ -48,6 +48,10 @@ const DeviceInfo* current_device_info();
 int launch_cooperative(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                        void** params, const char* what);
 
+// Makes sure `kernel` may be launched with `bytes` of dynamic shared memory (driver call made once
+// per device, kernel and size, not per launch).
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 // Number of CTAs of `kernel` that fit on one SM (cached by the callers).
 int max_ctas_per_sm(const void* kernel, int threads, size_t smem);
 

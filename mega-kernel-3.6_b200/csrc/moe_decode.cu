@@ -716,7 +716,8 @@ int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* works
         int tb = 1;
         while (tb < ntok) tb <<= 1;
         const void* kernel = moe_kernel(a->dtype, tb);
-        MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
+        rc = ensure_dynamic_smem(kernel, plan.smem_bytes);
+        if (rc != MK36_OK) return rc;
         p.ntok = ntok;
         p.x = static_cast<const unsigned char*>(a->x) + (size_t)b0 * a->hidden * es;
         p.out = a->out ? static_cast<unsigned char*>(a->out) + (size_t)b0 * a->hidden * es : nullptr;

@@ -1281,7 +1281,10 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
 
     const void* kernel = (a->dtype == MK36_BF16) ? (const void*)moe_decode_ring_kernel<__nv_bfloat16>
                                                  : (const void*)moe_decode_ring_kernel<__half>;
-    MK36_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    {
+        const int rc_smem = ensure_dynamic_smem(kernel, smem_bytes);
+        if (rc_smem != MK36_OK) return rc_smem;
+    }
     const size_t es = 2;
     for (int b0 = 0; b0 < a->batch; b0 += tb) {
         p.ntok = (a->batch - b0 < tb) ? (a->batch - b0) : tb;
