@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "moe_decode.cu",
     "moe_decode_ring.cu",
     "dense_ffn_decode.cu",
+    "dense_ffn_mma.cu",
     "attention_decode.cu",
     "attention_decode_mma.cu",
     "attention_decode_static.cu",

@@ -8,6 +8,8 @@
 
 namespace mk36 {
 int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int dense_ffn_mma_launch(const mk36_dense_ffn_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                         bool* handled);
 }
 
 using namespace mk36;
@@ -38,6 +40,17 @@ int to_moe_args(const mk36_dense_ffn_args* a, mk36_moe_args* m) {
     return MK36_OK;
 }
 
+// The tensor-core kernel when the shapes suit it, else the shared-expert-only mode of the MoE kernel.
+int dense_launch(const mk36_dense_ffn_args* a, const mk36_moe_args* m, const mk36_comm* comm, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream) {
+    if (!options().force_generic) {
+        bool handled = false;
+        const int rc = dense_ffn_mma_launch(a, comm, workspace, workspace_bytes, stream, &handled);
+        if (rc != MK36_OK || handled) return rc;
+    }
+    return moe_decode_launch(m, comm, workspace, workspace_bytes, stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -52,7 +65,7 @@ int mk36_dense_ffn_decode(const mk36_dense_ffn_args* args, void* workspace, size
     mk36_moe_args m;
     int rc = to_moe_args(args, &m);
     if (rc != MK36_OK) return rc;
-    return moe_decode_launch(&m, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    return dense_launch(args, &m, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int mk36_dense_ffn_decode_tp(const mk36_dense_ffn_args* args, const mk36_comm* comm, void* workspace, size_t workspace_bytes,
@@ -61,7 +74,7 @@ int mk36_dense_ffn_decode_tp(const mk36_dense_ffn_args* args, const mk36_comm* c
     mk36_moe_args m;
     int rc = to_moe_args(args, &m);
     if (rc != MK36_OK) return rc;
-    return moe_decode_launch(&m, comm, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    return dense_launch(args, &m, comm, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
