@@ -31,7 +31,7 @@ constexpr int kDenseWarps = 16;
 constexpr int kDenseThreads = kDenseWarps * 32;
 constexpr int kDenseMaxTokens = 8;
 constexpr int kDenseMaxTiles = 3;   // 16-row output tiles per CTA
-constexpr int kDenseAhead = 4;      // 32-wide slices of phase A in flight per warp
+constexpr int kDenseAhead = 8;      // 32-wide slices of phase A in flight per warp
 
 struct DenseMmaParams {
     const void* x;
@@ -84,36 +84,50 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_ffn_mma_kernel(const D
     const T* nw = static_cast<const T*>(p.norm_w);
     const size_t H = (size_t)p.H, I = (size_t)p.I;
 
-    // ---- phase 0: RMSNorm (a warp per token) ----
-    for (int b = warp; b < kDenseMaxTokens; b += kDenseWarps) {
-        T* dst = xs + (size_t)b * H;
-        if (b >= p.ntok) {
-            for (int k = lane * 8; k < p.H; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
-            continue;
-        }
-        const T* xr = x + (size_t)b * H;
+    // ---- phase 0: RMSNorm; the 16 warps are shared out over the tokens (16, 8, 4 or 2 warps per token) ----
+    {
+        __shared__ float s_part[kDenseWarps];
+        int tp2 = 1;
+        while (tp2 < p.ntok) tp2 <<= 1;
+        const int wpt = kDenseWarps / tp2;          // warps per token
+        const int b = warp / wpt, part = warp - b * wpt;
+        const int nchunk = p.H >> 3, stride = wpt * 32;
+        const bool live = b < p.ntok;
+        const T* xr = x + (size_t)(live ? b : 0) * H;
         float ss = 0.0f;
-        for (int k = lane * 8; k < p.H; k += 256) {
-            Chunk8<T> c;
-            c.raw = *reinterpret_cast<const uint4*>(xr + k);
-            float f[8];
-            unpack8(c, f);
+        if (live) {
+            for (int c = part * 32 + lane; c < nchunk; c += stride) {
+                Chunk8<T> v;
+                v.raw = *reinterpret_cast<const uint4*>(xr + 8 * c);
+                float f[8];
+                unpack8(v, f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+                for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+            }
         }
         ss = warp_sum(ss);
-        const float rstd = 1.0f / sqrtf(ss / (float)p.H + p.eps);
-        for (int k = lane * 8; k < p.H; k += 256) {
-            Chunk8<T> c, w;
-            c.raw = *reinterpret_cast<const uint4*>(xr + k);
-            w.raw = *reinterpret_cast<const uint4*>(nw + k);
-            float f[8], wf[8];
-            unpack8(c, f);
-            unpack8(w, wf);
-            T o[8];
+        if (lane == 0) s_part[warp] = ss;
+        // columns beyond the batch are zero
+        for (int idx = tid; idx < (kDenseMaxTokens - p.ntok) * nchunk; idx += kDenseThreads)
+            *reinterpret_cast<uint4*>(xs + (size_t)p.ntok * H + 8 * (size_t)idx) = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+        if (live) {
+            float tot = 0.0f;
+            for (int w = 0; w < wpt; ++w) tot += s_part[b * wpt + w];
+            const float rstd = 1.0f / sqrtf(tot / (float)p.H + p.eps);
+            T* dst = xs + (size_t)b * H;
+            for (int c = part * 32 + lane; c < nchunk; c += stride) {
+                Chunk8<T> v, w;
+                v.raw = *reinterpret_cast<const uint4*>(xr + 8 * c);
+                w.raw = *reinterpret_cast<const uint4*>(nw + 8 * c);
+                float f[8], wf[8];
+                unpack8(v, f);
+                unpack8(w, wf);
+                T o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = from_float<T>(__fmul_rn(__fmul_rn(f[i], rstd), wf[i]));
-            *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(o);
+                for (int i = 0; i < 8; ++i) o[i] = from_float<T>(__fmul_rn(__fmul_rn(f[i], rstd), wf[i]));
+                *reinterpret_cast<uint4*>(dst + 8 * c) = *reinterpret_cast<const uint4*>(o);
+            }
         }
     }
     __syncthreads();
