@@ -245,6 +245,17 @@ def bench_others(device, steps: int, warmup: int, peak, only=None):
         fns = [(lambda i=i: mk.linear_attention_decode(ins[i % copies])) for i in range(n)]
         ms, _, _ = time_graph(fns, warmup)
         record(f"linear_attention_b{batch}", ms, n, syn.linear_algorithmic_bytes(batch, 16, 32, 128, 128))
+        # resident-state variant: 64 steps per launch, the state crosses HBM twice per launch; reported per
+        # step under its own name (its per-step bytes are q, k, v, out plus 1/64 of the state traffic)
+        nsteps = 64
+        seq = list(syn.linear_step_stream(batch, 16, 32, 128, 128, steps=nsteps, seed=1))
+        qs, ks, vs = (torch.stack([s_[n_] for s_ in seq]).to(device) for n_ in ("q", "k", "v"))
+        mk.linear_attention_decode_steps(qs, ks, vs, states[0], decay=0.9)
+        n2 = max(4, min(copies, 16))
+        fns = [(lambda i=i: mk.linear_attention_decode_steps(qs, ks, vs, states[i % copies], decay=0.9)) for i in range(n2)]
+        ms, _, _ = time_graph(fns, min(warmup, 3))
+        per_step_bytes = (2 * batch * 32 * 128 * 128 * 4) // nsteps + batch * (2 * 16 * 128 + 2 * 32 * 128) * 2
+        record(f"linear_attention_b{batch}_resident_{nsteps}steps_per_step", ms, n2 * nsteps, per_step_bytes)
         del states, ins
         torch.cuda.empty_cache()
     return out

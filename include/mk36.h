@@ -278,6 +278,36 @@ typedef struct mk36_linear_attention_args {
 
 MK36_API int mk36_linear_attention_decode(const mk36_linear_attention_args* args, void* stream);
 
+/* Several consecutive steps of the same recurrence in one call, the fp32 state resident on chip:
+ * q, k are [steps, batch, key_heads, key_dim], v and out [steps, batch, value_heads, value_dim];
+ * step t reads its q/k/v, updates the state and writes out[t]; the state is read from `state` once and
+ * written to `new_state` once (they may be the same buffer).  decay_per_step / beta_per_step are
+ * optional fp32 [steps, batch, value_heads] gates (NULL: the scalar `decay`, beta 1).  Outputs
+ * and final state are bit-identical to `steps` calls of mk36_linear_attention_decode.  The reference's
+ * operator is one step per call (mega_kernel_qwen36/ops.py:377-386), so this entry point has no
+ * counterpart there; it exists because a one-step call has to move the whole state (2 MiB per
+ * batch row at the 35B-A3B shape) through HBM twice per token. */
+typedef struct mk36_linear_attention_steps_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    const float* state;
+    void* out;
+    float* new_state;
+    const float* decay_per_step;
+    const float* beta_per_step;
+    int32_t dtype; /* of q, k, v, out */
+    int32_t steps;
+    int32_t batch;
+    int32_t key_heads;
+    int32_t value_heads;
+    int32_t key_dim;
+    int32_t value_dim;
+    float decay;
+} mk36_linear_attention_steps_args;
+
+MK36_API int mk36_linear_attention_decode_steps(const mk36_linear_attention_steps_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Multi-GPU (one process per GPU, all GPUs on one NVLink / NVSwitch box).
  *

@@ -435,6 +435,60 @@ std::tuple<torch::Tensor, torch::Tensor> linear_attention_decode_ex(torch::Tenso
     return linear_attention_impl(q, k, v, state, decay, decay_per_head, beta_per_head, inplace, true);
 }
 
+// Several steps in one call with the state resident on chip: q, k [steps, batch, key_heads, key_dim],
+// v [steps, batch, value_heads, value_dim]; returns (out [steps, batch, value_heads, value_dim], new_state).
+std::tuple<torch::Tensor, torch::Tensor> linear_attention_decode_steps(torch::Tensor q, torch::Tensor k, torch::Tensor v,
+                                                                       torch::Tensor state, double decay,
+                                                                       std::optional<torch::Tensor> decay_per_step,
+                                                                       std::optional<torch::Tensor> beta_per_step, bool inplace) {
+    SHIM_CHECK_INPUT(q);
+    SHIM_CHECK_INPUT(k);
+    SHIM_CHECK_INPUT(v);
+    SHIM_CHECK_INPUT(state);
+    TORCH_CHECK(q.dim() == 4, "q must be [steps, batch, heads, key_dim]");
+    TORCH_CHECK(k.sizes() == q.sizes(), "k shape must match q");
+    TORCH_CHECK(v.dim() == 4, "v must be [steps, batch, heads, value_dim]");
+    TORCH_CHECK(state.dim() == 4, "state must be [batch, heads, key_dim, value_dim]");
+    TORCH_CHECK(state.scalar_type() == torch::kFloat32, "state must be float32");
+    TORCH_CHECK(q.scalar_type() == k.scalar_type(), "q and k dtype mismatch");
+    TORCH_CHECK(q.scalar_type() == v.scalar_type(), "q and v dtype mismatch");
+    const int64_t steps = q.size(0), batch = q.size(1), key_heads = q.size(2), key_dim = q.size(3);
+    const int64_t value_heads = v.size(2), value_dim = v.size(3);
+    TORCH_CHECK(steps > 0, "at least one step is required");
+    TORCH_CHECK(v.size(0) == steps && v.size(1) == batch && value_heads % key_heads == 0, "v steps/batch/head mismatch");
+    TORCH_CHECK(state.size(0) == batch && state.size(1) == value_heads && state.size(2) == key_dim && state.size(3) == value_dim,
+                "state shape mismatch");
+    const c10::cuda::CUDAGuard guard(q.device());
+    mk36_linear_attention_steps_args a{};
+    auto gate = [&](const std::optional<torch::Tensor>& g, const char* name) -> const float* {
+        if (!g.has_value()) return nullptr;
+        const torch::Tensor& d = *g;
+        TORCH_CHECK(d.is_cuda() && d.is_contiguous() && d.scalar_type() == torch::kFloat32 && d.numel() == steps * batch * value_heads,
+                    name, " must be a contiguous float32 CUDA tensor [steps, batch, value_heads]");
+        return d.data_ptr<float>();
+    };
+    a.decay_per_step = gate(decay_per_step, "decay_per_step");
+    a.beta_per_step = gate(beta_per_step, "beta_per_step");
+    auto out = torch::empty({steps, batch, value_heads, value_dim}, q.options());
+    torch::Tensor new_state = inplace ? state : torch::empty_like(state);
+    a.q = q.data_ptr();
+    a.k = k.data_ptr();
+    a.v = v.data_ptr();
+    a.state = state.data_ptr<float>();
+    a.out = out.data_ptr();
+    a.new_state = new_state.data_ptr<float>();
+    a.dtype = dtype_code(q, "linear_attention_decode_steps");
+    a.steps = static_cast<int32_t>(steps);
+    a.batch = static_cast<int32_t>(batch);
+    a.key_heads = static_cast<int32_t>(key_heads);
+    a.value_heads = static_cast<int32_t>(value_heads);
+    a.key_dim = static_cast<int32_t>(key_dim);
+    a.value_dim = static_cast<int32_t>(value_dim);
+    a.decay = static_cast<float>(decay);
+    check_rc(mk36_linear_attention_decode_steps(&a, at::cuda::getCurrentCUDAStream().stream()));
+    return std::make_tuple(out, new_state);
+}
+
 // Reads back the device status word of this device's workspace (synchronises the stream).
 int64_t workspace_status(torch::Tensor like) {
     SHIM_CHECK_CUDA(like);
@@ -471,6 +525,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("linear_attention_decode_ex", &linear_attention_decode_ex, "per-head decay/beta, grouped keys, optional in-place state",
           py::arg("q"), py::arg("k"), py::arg("v"), py::arg("state"), py::arg("decay") = 1.0,
           py::arg("decay_per_head") = py::none(), py::arg("beta_per_head") = py::none(), py::arg("inplace") = false);
+    m.def("linear_attention_decode_steps", &linear_attention_decode_steps, "several recurrent steps in one launch, state resident on chip",
+          py::arg("q"), py::arg("k"), py::arg("v"), py::arg("state"), py::arg("decay") = 1.0,
+          py::arg("decay_per_step") = py::none(), py::arg("beta_per_step") = py::none(), py::arg("inplace") = false);
     m.def("workspace_status", &workspace_status, "device status word of the workspace on the tensor's device");
     m.def("workspace_reset", &workspace_reset, "re-initialise the workspace on the tensor's device");
     m.def("library_version", []() { return mk36_version(); });

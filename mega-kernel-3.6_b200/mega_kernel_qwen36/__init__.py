@@ -37,6 +37,7 @@ from .ops import (
     full_attention_decode,
     linear_attention_decode,
     linear_attention_decode_gated,
+    linear_attention_decode_steps,
     moe_decode,
 )
 
@@ -65,6 +66,7 @@ __all__ = [
     "full_attention_decode",
     "linear_attention_decode",
     "linear_attention_decode_gated",
+    "linear_attention_decode_steps",
     "moe_decode",
     "qwen36_27b_config",
     "qwen36_35b_a3b_config",

@@ -61,6 +61,16 @@ class LinearAttentionArgs(C.Structure):
     ]
 
 
+class LinearAttentionStepsArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("state", C.c_void_p),
+        ("out", C.c_void_p), ("new_state", C.c_void_p), ("decay_per_step", C.c_void_p),
+        ("beta_per_step", C.c_void_p),
+        ("dtype", C.c_int32), ("steps", C.c_int32), ("batch", C.c_int32), ("key_heads", C.c_int32),
+        ("value_heads", C.c_int32), ("key_dim", C.c_int32), ("value_dim", C.c_int32), ("decay", C.c_float),
+    ]
+
+
 MK36_MAX_RANKS = 8
 MK36_IPC_HANDLE_BYTES = 64
 
@@ -88,6 +98,7 @@ SIGNATURES = {
     "mk36_full_attention_decode": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_full_attention_decode_static": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
     "mk36_linear_attention_decode": (C.c_int, [C.POINTER(LinearAttentionArgs), C.c_void_p]),
+    "mk36_linear_attention_decode_steps": (C.c_int, [C.POINTER(LinearAttentionStepsArgs), C.c_void_p]),
     "mk36_comm_buffer_bytes": (C.c_size_t, []),
     "mk36_comm_buffer_alloc": (C.c_int, [C.POINTER(C.c_void_p)]),
     "mk36_comm_buffer_free": (C.c_int, [C.c_void_p]),

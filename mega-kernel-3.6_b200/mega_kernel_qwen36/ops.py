@@ -230,6 +230,29 @@ def linear_attention_decode_gated(
     )
 
 
+def linear_attention_decode_steps(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    state: torch.Tensor,
+    *,
+    decay: float = 1.0,
+    decay_per_step: Optional[torch.Tensor] = None,
+    beta_per_step: Optional[torch.Tensor] = None,
+    inplace: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Several consecutive steps of the recurrence in one launch with the fp32 state resident on
+    chip: ``q, k`` are ``[steps, B, Hk, Dk]``, ``v`` is ``[steps, B, Hv, Dv]``; returns
+    ``(out[steps, B, Hv, Dv], final_state)``.  Bit-identical to ``steps`` calls of
+    ``linear_attention_decode`` / ``linear_attention_decode_gated`` (the gates are then
+    ``[steps, B, Hv]``), but the state crosses HBM twice per call instead of twice per step."""
+    ext = _native("linear_attention_decode_steps", q, k, v, state)
+    return ext.linear_attention_decode_steps(
+        q.contiguous(), k.contiguous(), v.contiguous(), state if inplace else state.contiguous(),
+        float(decay), decay_per_step, beta_per_step, bool(inplace),
+    )
+
+
 def decode_layer(
     layer_idx: int,
     hidden: torch.Tensor,
