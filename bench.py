@@ -47,8 +47,8 @@ NOMINAL_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (57.77 MB read + 0.58 MB written; None where no capture exists).
-NCU_TRAFFIC_BYTES = {"moe_b1": 58_354_000}
+# capture summarised under profiles/ (57.80 MB read + 0.3-0.8 MB written; None where no capture exists).
+NCU_TRAFFIC_BYTES = {"moe_b1": 58_350_000}
 
 
 def measured_peak():
