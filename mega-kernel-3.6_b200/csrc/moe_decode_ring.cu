@@ -312,8 +312,11 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long m, int q) {
     return __ffsll((long long)m) - 1;
 }
 
-template <typename T>
+template <typename T, bool SC>
 __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const MoeRingParams p) {
+    // SC: plain-FMA consumers (launches of one or two tokens) or tensor-core consumers.  A template
+    // parameter, not a run-time flag: the kernel runs every code path about once, so the size of the
+    // code it has to fetch shows in its time, and each instantiation carries only its own path.
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_flag;
     __shared__ int s_unique;
@@ -561,7 +564,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         bool got = ok;
         if (got) got = mbar_wait(&full_bar[stage], use_of(n) & 1, &s_abort);
         if (!got) ok = false;
-        if (p.scalar) {
+        if (SC) {
             // a warp takes whole rows (router) or whole (gate, up) pairs: nothing to combine across warps
             if (got) {
                 const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kRingStageBytes);
@@ -894,7 +897,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
             for (int q = 0; q < kActBatch; ++q) {
                 if (dst[q] >= 0) {
                     const float in[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
-                    if (p.scalar) {
+                    if (SC) {
                         *reinterpret_cast<float4*>(actf + dst[q]) = v[q];
                         continue;
                     }
@@ -916,7 +919,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
     // ---- phase C: down rows.  part[slot][row]: slot < npairs routed pairs, then one per token (shared).
     //      One warp contracts one expert's block of rows over the whole intermediate length. ----
     const int nC = nC_all;
-    if (p.scalar) {
+    if (SC) {
         // at most two tokens in the launch (see the host side): a row meets at most two activation vectors
         const int nchI = p.I >> 3, nchIs = p.Is >> 3;
         const int ndc = min(p.nded, nC);
@@ -1251,8 +1254,9 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
     p.fd_epc = make_fastdiv(epc);
     p.fd_ks = make_fastdiv(kRingGroupWarps / epc);
 
-    const void* kernel = (a->dtype == MK36_BF16) ? (const void*)moe_decode_ring_kernel<__nv_bfloat16>
-                                                 : (const void*)moe_decode_ring_kernel<__half>;
+    const void* kernel = (a->dtype == MK36_BF16)
+                             ? (p.scalar ? (const void*)moe_decode_ring_kernel<__nv_bfloat16, true> : (const void*)moe_decode_ring_kernel<__nv_bfloat16, false>)
+                             : (p.scalar ? (const void*)moe_decode_ring_kernel<__half, true> : (const void*)moe_decode_ring_kernel<__half, false>);
     {
         const int rc_smem = ensure_dynamic_smem(kernel, smem_bytes);
         if (rc_smem != MK36_OK) return rc_smem;
