@@ -197,3 +197,41 @@ def test_algorithmic_byte_formulas():
     assert syn.attention_algorithmic_bytes(1, 16, 2, 256, 32768) == 67_125_248
     assert syn.attention_algorithmic_bytes(1, 16, 2, 256, 4096) == 8_404_992
     assert syn.linear_algorithmic_bytes(8, 16, 32, 128, 128) == 33_751_040
+
+
+def test_ctypes_structures_match_the_c_header(tmp_path):
+    """Size and field offsets of every argument struct, as the C compiler sees include/mk36.h,
+    against the ctypes mirror in cabi.py (a drifted field would otherwise only show on a GPU)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc") or shutil.which("cc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    pairs = {
+        "mk36_moe_args": cabi.MoeArgs,
+        "mk36_dense_ffn_args": cabi.DenseFfnArgs,
+        "mk36_attention_args": cabi.AttentionArgs,
+        "mk36_linear_attention_args": cabi.LinearAttentionArgs,
+        "mk36_linear_attention_steps_args": cabi.LinearAttentionStepsArgs,
+        "mk36_comm": cabi.Comm,
+    }
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "mk36.h"', "int main(void) {"]
+    for cname, ctype in pairs.items():
+        lines.append(f'printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in ctype._fields_:
+            lines.append(f'printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["return 0; }"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = {}
+    for line in out.splitlines():
+        cname, field, value = line.split()
+        seen[(cname, field)] = int(value)
+    for cname, ctype in pairs.items():
+        assert seen[(cname, "size")] == __import__("ctypes").sizeof(ctype), cname
+        for field, _ in ctype._fields_:
+            assert seen[(cname, field)] == getattr(ctype, field).offset, f"{cname}.{field}"
