@@ -134,45 +134,73 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_ffn_mma_kernel(const D
     if (tracer) trace_stamp(p.ctl, 1);
 
     // ---- phase A: gate/up tiles ----
+    // The CTA owns a contiguous range of tiles.  When it has fewer tiles than warps (a tensor-parallel
+    // shard), ks = 2, 4, 8 or 16 warps share a tile and split the hidden length, so that all warps keep
+    // streaming; their partial sums meet in shared memory before SiLU.
     {
+        __shared__ float4 s_parta[kDenseThreads];
         const T* gw = static_cast<const T*>(p.gate);
         const T* uw = static_cast<const T*>(p.up);
         const int ntiles = p.I >> 3;
         const int nsl = p.H >> 5;  // 32-wide slices of the contraction
+        const int t_lo = (int)(((long long)ntiles * cta) / ncta), t_hi = (int)(((long long)ntiles * (cta + 1)) / ncta);
+        const int nt = t_hi - t_lo;
+        int ks = 1;
+        while (ks < kDenseWarps && nt * (ks * 2) <= kDenseWarps) ks <<= 1;
+        const int per_round = kDenseWarps / ks;
+        const int kpart = warp & (ks - 1), tslot = warp / ks;
+        const int sa = (int)(((long long)nsl * kpart) / ks), sb = (int)(((long long)nsl * (kpart + 1)) / ks);
         const T* bcol = xs + (size_t)g * H + 8 * t;
-        for (int tile = cta * kDenseWarps + warp; tile < ntiles; tile += ncta * kDenseWarps) {
+        for (int r0 = 0; r0 < nt; r0 += per_round) {  // the same trip count for every warp of the CTA
+            const bool live = r0 + tslot < nt;
+            const int tile = t_lo + (live ? r0 + tslot : 0);
             const T* ga = gw + ((size_t)tile * 8 + g) * H + 8 * t;
             const T* ua = uw + ((size_t)tile * 8 + g) * H + 8 * t;
             float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-            uint4 qa[kDenseAhead], qb[kDenseAhead];
-#pragma unroll
-            for (int j = 0; j < kDenseAhead; ++j) {
-                if (j < nsl) {
-                    qa[j] = ldg_stream(ga + 32 * j);
-                    qb[j] = ldg_stream(ua + 32 * j);
-                }
-            }
-            for (int s0 = 0; s0 < nsl; s0 += kDenseAhead) {
+            if (live) {
+                uint4 qa[kDenseAhead], qb[kDenseAhead];
 #pragma unroll
                 for (int j = 0; j < kDenseAhead; ++j) {
-                    const int s = s0 + j;
-                    if (s < nsl) {
-                        const uint4 a = qa[j], b = qb[j];
-                        const int nx = s + kDenseAhead;
-                        if (nx < nsl) {  // refill this slot before using its old contents
-                            qa[j] = ldg_stream(ga + 32 * nx);
-                            qb[j] = ldg_stream(ua + 32 * nx);
+                    if (sa + j < sb) {
+                        qa[j] = ldg_stream(ga + 32 * (sa + j));
+                        qb[j] = ldg_stream(ua + 32 * (sa + j));
+                    }
+                }
+                for (int s0 = sa; s0 < sb; s0 += kDenseAhead) {
+#pragma unroll
+                    for (int j = 0; j < kDenseAhead; ++j) {
+                        const int s = s0 + j;
+                        if (s < sb) {
+                            const uint4 a = qa[j], b = qb[j];
+                            const int nx = s + kDenseAhead;
+                            if (nx < sb) {  // refill this slot before using its old contents
+                                qa[j] = ldg_stream(ga + 32 * nx);
+                                qb[j] = ldg_stream(ua + 32 * nx);
+                            }
+                            const uint4 xv = *reinterpret_cast<const uint4*>(bcol + 32 * s);
+                            mma_slice32<T>(d0, d1, a, b, xv);
                         }
-                        const uint4 xv = *reinterpret_cast<const uint4*>(bcol + 32 * s);
-                        mma_slice32<T>(d0, d1, a, b, xv);
                     }
                 }
             }
             // rows g (gate) and g + 8 (up) of channel 8 * tile + g, tokens 2t and 2t + 1
-            const int ch = tile * 8 + g;
-            const float g0 = d0[0] + d1[0], g1 = d0[1] + d1[1], u0 = d0[2] + d1[2], u1 = d0[3] + d1[3];
-            if (2 * t < p.ntok) p.act[(size_t)(2 * t) * I + ch] = silu(g0) * u0;
-            if (2 * t + 1 < p.ntok) p.act[(size_t)(2 * t + 1) * I + ch] = silu(g1) * u1;
+            float g0 = d0[0] + d1[0], g1 = d0[1] + d1[1], u0 = d0[2] + d1[2], u1 = d0[3] + d1[3];
+            if (ks > 1) {
+                s_parta[tid] = make_float4(g0, g1, u0, u1);
+                __syncthreads();
+                if (kpart == 0) {
+                    for (int q = 1; q < ks; ++q) {
+                        const float4 o = s_parta[tid + 32 * q];
+                        g0 += o.x; g1 += o.y; u0 += o.z; u1 += o.w;
+                    }
+                }
+                __syncthreads();  // the partials have been read before the next round overwrites them
+            }
+            if (live && kpart == 0) {
+                const int ch = tile * 8 + g;
+                if (2 * t < p.ntok) p.act[(size_t)(2 * t) * I + ch] = silu(g0) * u0;
+                if (2 * t + 1 < p.ntok) p.act[(size_t)(2 * t + 1) * I + ch] = silu(g1) * u1;
+            }
         }
     }
     if (tracer) trace_stamp(p.ctl, 2);

@@ -65,7 +65,7 @@ def test_static_scratch_entry_matches_workspace_entry_on_consecutive_calls(cuda_
             outs.append(out)
         torch.cuda.synchronize()
         for i, out in enumerate(outs):
-            parity.assert_output_parity(out.float().cpu(), expect.float().cpu(), f"static call {i} {shape}")
+            parity.assert_output_parity(out.cpu(), expect.cpu(), f"static call {i} {shape}")
         # same kernels, same split plan: in fact the results are identical
         assert torch.equal(outs[0], outs[1])
         assert torch.equal(outs[0], expect)
@@ -85,8 +85,8 @@ def test_static_scratch_entry_two_problems_in_a_row_without_sync(cuda_device):
     cabi.check(lib.mk36_full_attention_decode_static(_args(cabi, ta, oa, *shape_a, cabi.MK36_BF16), stream))
     cabi.check(lib.mk36_full_attention_decode_static(_args(cabi, tb, ob, *shape_b, cabi.MK36_BF16), stream))
     torch.cuda.synchronize()
-    parity.assert_output_parity(oa.float().cpu(), ea.float().cpu(), "first queued problem")
-    parity.assert_output_parity(ob.float().cpu(), eb.float().cpu(), "second queued problem")
+    parity.assert_output_parity(oa.cpu(), ea.cpu(), "first queued problem")
+    parity.assert_output_parity(ob.cpu(), eb.cpu(), "second queued problem")
 
 
 def test_static_scratch_entry_argument_errors(cuda_device):
