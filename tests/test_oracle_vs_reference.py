@@ -1,6 +1,6 @@
 """The CPU oracle against the reference's reference.py imported live from a reference checkout.
 
-Runs only where the checkout exists (set MK36_REFERENCE_ROOT, default /root/reference); elsewhere
+Runs only where the checkout exists (MK36_REFERENCE_ROOT points at it; see REF_ROOT below); elsewhere
 the committed fixtures (tests/test_golden.py) carry the same pin.  Seeds here differ from the
 fixture seeds on purpose.
 """
