@@ -189,6 +189,21 @@ def test_c_abi_argument_errors_need_no_gpu():
     assert lib.mk36_linear_attention_decode(la, None) == cabi.MK36_ERR_INVALID_ARG
     assert b"multiple of key_heads" in lib.mk36_last_error()
     assert lib.mk36_workspace_init(None, 0, None) == cabi.MK36_ERR_WORKSPACE
+    # multi-step recurrence and the multi-GPU entry points refuse bad descriptors before touching a device
+    ls = cabi.LinearAttentionStepsArgs(q=1, k=1, v=1, state=1, out=1, new_state=1, dtype=0, steps=0, batch=1, key_heads=2,
+                                       value_heads=4, key_dim=8, value_dim=8, decay=1.0)
+    assert lib.mk36_linear_attention_decode_steps(ls, None) == cabi.MK36_ERR_INVALID_ARG
+    assert b"sizes must be positive" in lib.mk36_last_error()
+    ls.steps, ls.key_heads = 4, 3
+    assert lib.mk36_linear_attention_decode_steps(ls, None) == cabi.MK36_ERR_INVALID_ARG
+    assert lib.mk36_moe_decode_ep(None, None, None, 0, None) == cabi.MK36_ERR_INVALID_ARG
+    assert b"comm is NULL" in lib.mk36_last_error()
+    assert lib.mk36_dense_ffn_decode_tp(None, None, None, 0, None) == cabi.MK36_ERR_INVALID_ARG
+    assert lib.mk36_ipc_export(None, None) == cabi.MK36_ERR_INVALID_ARG
+    assert lib.mk36_ipc_open(None, None) == cabi.MK36_ERR_INVALID_ARG
+    assert lib.mk36_comm_buffer_alloc(None) == cabi.MK36_ERR_INVALID_ARG
+    assert lib.mk36_comm_buffer_bytes() >= 2 * 8 * 8 * 8192 * 8
+    assert lib.mk36_full_attention_decode_static(None, None) == cabi.MK36_ERR_INVALID_ARG
 
 
 def test_algorithmic_byte_formulas():
