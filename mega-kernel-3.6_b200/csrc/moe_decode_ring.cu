@@ -432,7 +432,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
         if (s_abort != 0) ok = false;
         if (lane == 0 && ok) {
             const int tasks = p.I * n_unique;
-            const int t0 = fdiv(tasks * cta, p.fd_ncta), t1 = fdiv(tasks * (cta + 1), p.fd_ncta);
+            // whole chunks per CTA (a chunk never straddles two CTAs: a partial chunk costs a full stage round trip)
+    const int nch_all = fdiv(tasks, p.fd_pr);
+    const int t0 = fdiv(nch_all * cta, p.fd_ncta) * PR, t1 = fdiv(nch_all * (cta + 1), p.fd_ncta) * PR;
             const int nB = chunks_in(t0, t1, p.fd_pr);
             const int mB = fdiv(t0, p.fd_pr);
             const int nC = (hr > 0) ? fdiv(n_unique + p.epc - 1, p.fd_epc) : 0;
@@ -820,7 +822,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) moe_decode_ring_kernel(const 
 
     // ---- phase B: routed gate+up rows -> silu(g) * u per (pair, channel) ----
     const int tasks = p.I * n_unique;
-    const int t0 = fdiv(tasks * cta, p.fd_ncta), t1 = fdiv(tasks * (cta + 1), p.fd_ncta);
+    // whole chunks per CTA (a chunk never straddles two CTAs: a partial chunk costs a full stage round trip)
+    const int nch_all = fdiv(tasks, p.fd_pr);
+    const int t0 = fdiv(nch_all * cta, p.fd_ncta) * PR, t1 = fdiv(nch_all * (cta + 1), p.fd_ncta) * PR;
     const int nB = chunks_in(t0, t1, p.fd_pr);
     const int mB = fdiv(t0, p.fd_pr);
     for (int k = 0; k < nB; ++k) {
