@@ -13,7 +13,9 @@
  *     are asynchronous with respect to the host;
  *   - entry points return MK36_OK (0) or a negative mk36_status; mk36_last_error() then holds a
  *     human-readable message for the calling thread;
- *   - the library never allocates or frees device memory.  Kernels that need scratch memory or
+ *   - the decode entry points never allocate or free device memory (the one allocation the library
+ *     owns is the multi-GPU exchange buffer of mk36_comm_buffer_alloc, made once at set-up).
+ *     Kernels that need scratch memory or
  *     a grid-wide barrier take a caller-owned `workspace` (see mk36_workspace_*).  A workspace
  *     must not be used by two kernels that may run concurrently (use one per stream);
  *   - inputs are never written.
