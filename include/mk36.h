@@ -80,7 +80,7 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
 /* Process-wide switches.  "force_generic" = 1 makes every op use its general register-streaming
  * kernel even where a specialised shared-memory-ring variant exists (the variants compute the same
  * function; tests use the switch to cover both).  "ring_mma" = 1 makes the MoE ring kernel contract
- * with tensor-core instructions whatever the token count (by default launches of up to four tokens
+ * with tensor-core instructions whatever the token count (by default launches of one or two tokens
  * use plain FMAs, which is faster there).  Unknown names return MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 
