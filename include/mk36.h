@@ -67,8 +67,13 @@ MK36_API const char* mk36_last_error(void);
  *
  * mk36_workspace_bytes()       size that is enough for every op at the measured shapes
  *                              (batch <= 8 per launch); 256-byte alignment is required.
- * mk36_workspace_init()        zeroes the control block (barrier counters, status word).  Must
- *                              run once before first use and after any reported timeout.
+ * mk36_workspace_init()        zeroes the control block (first 32 KB: barrier counters, status
+ *                              word, epoch) and, when the workspace reaches that far, the 1 MiB of
+ *                              mailboxes at offset 16 MiB through which the MoE stream kernel
+ *                              passes router logits between CTAs.  Must run once before first use
+ *                              and after any reported timeout: a set status word is sticky, every
+ *                              later kernel on the workspace leaves at once without writing its
+ *                              outputs until the workspace has been initialised again.
  * mk36_workspace_status()      synchronises `stream` and returns the device status word in
  *                              *device_status: 0 = clean, otherwise the code of the bounded wait
  *                              that gave up (MK36_ERR_BARRIER_TIMEOUT is returned as well).
@@ -79,9 +84,12 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
 
 /* Process-wide switches.  "force_generic" = 1 makes every op use its general register-streaming
  * kernel even where a specialised shared-memory-ring variant exists (the variants compute the same
- * function; tests use the switch to cover both).  "ring_mma" = 1 makes the MoE ring kernel contract
- * with tensor-core instructions whatever the token count (by default launches of one or two tokens
- * use plain FMAs, which is faster there).  Unknown names return MK36_ERR_INVALID_ARG. */
+ * function; tests use the switch to cover both).  MoE calls of one or two tokens normally run the
+ * stream kernel (no grid barrier before the routing, dealt gate/up chunks); "moe_stream" = 0 sends
+ * them to the ring kernel instead, "ring_mma" = 1 additionally makes the ring kernel contract with
+ * tensor-core instructions whatever the token count.  "moe_stages" (0 = default, else 2..6) sets the
+ * stream kernel's ring depth and "moe_static" = 1 makes it deal its chunks without the work counter;
+ * both exist for measurements.  Unknown names return MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 
 /* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase
@@ -90,10 +98,10 @@ MK36_API int mk36_set_option(const char* name, int value);
  * `stamps`.  The reference has no tracing beyond CUDA-event timers (benchmarks/bench_utils.py:17-56). */
 MK36_API int mk36_workspace_trace(void* workspace, void* stream, unsigned long long* stamps, int count);
 
-/* Per-CTA stamps: thread 0 of every CTA of a persistent kernel records the GPU timer at up to four
- * phase boundaries (MoE: end of routed gate/up, after the second grid barrier, end of down rows, exit).
- * Copies 4 stamps for each of the first `ctas` (<= 384) CTAs to the HOST array `stamps`
- * [ctas][4] after synchronising `stream`; the spread across CTAs shows load imbalance. */
+/* Per-CTA stamps: thread 0 of every CTA of a persistent kernel records the GPU timer at up to eight
+ * phase boundaries (MoE: 0 end of routed gate/up, 1 after the grid barrier, 2 end of down rows, 3 entry,
+ * 4 logits published).  Copies 8 stamps for each of the first `ctas` (<= 192) CTAs to the HOST array
+ * `stamps` [ctas][8] after synchronising `stream`; the spread across CTAs shows load imbalance. */
 MK36_API int mk36_workspace_cta_trace(void* workspace, void* stream, unsigned long long* stamps, int ctas);
 
 /* Test hook for the give-up path of the bounded device-side waits: launches two CTAs whose barrier

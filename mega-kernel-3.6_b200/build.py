@@ -32,6 +32,7 @@ CUDA_SOURCES = [
     "mk36_comm.cu",
     "moe_decode.cu",
     "moe_decode_ring.cu",
+    "moe_decode_stream.cu",
     "dense_ffn_decode.cu",
     "dense_ffn_mma.cu",
     "attention_decode.cu",

@@ -128,6 +128,9 @@ int mk36_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
     if (workspace_bytes < kControlBytes) MK36_FAIL(MK36_ERR_WORKSPACE, "workspace smaller than its control block");
     if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) MK36_FAIL(MK36_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     MK36_CUDA_OK(cudaMemsetAsync(workspace, 0, kControlBytes, static_cast<cudaStream_t>(stream)));
+    // the mailboxes of the MoE stream kernel, when the workspace is large enough to hold them
+    if (workspace_bytes >= kTaggedEnd)
+        MK36_CUDA_OK(cudaMemsetAsync(static_cast<unsigned char*>(workspace) + kMailboxOffset, 0, kTaggedEnd - kMailboxOffset, static_cast<cudaStream_t>(stream)));
     return MK36_OK;
 }
 
@@ -150,6 +153,18 @@ int mk36_set_option(const char* name, int value) {
     }
     if (std::strcmp(name, "ring_mma") == 0) {
         options().ring_mma = value ? 1 : 0;
+        return MK36_OK;
+    }
+    if (std::strcmp(name, "moe_stream") == 0) {
+        options().moe_stream = value ? 1 : 0;
+        return MK36_OK;
+    }
+    if (std::strcmp(name, "moe_stages") == 0) {
+        options().moe_stages = value > 0 ? value : 0;
+        return MK36_OK;
+    }
+    if (std::strcmp(name, "moe_static") == 0) {
+        options().moe_static = value ? 1 : 0;
         return MK36_OK;
     }
     MK36_FAIL(MK36_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);

@@ -78,6 +78,9 @@ inline FastDiv make_fastdiv(unsigned d) {
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
     int ring_mma = 0;       // 1: the MoE ring kernel contracts with mma.sync whatever the token count
+    int moe_stream = 1;     // 0: launches of one or two tokens use the ring kernel instead of the stream kernel
+    int moe_stages = 0;     // > 0: ring depth of the MoE stream kernel (default: chosen from the shapes)
+    int moe_static = 0;     // 1: the MoE stream kernel deals its gate/up chunks statically (no work counter)
 };
 Options& options();
 
@@ -88,10 +91,11 @@ constexpr int kTraceSlots = 24;
 
 struct Control {
     unsigned int bar_count;   // barrier arrivals since the kernel started
-    unsigned int unused0;
-    int status;               // 0 or the code of the wait that gave up
+    unsigned int work_ticket; // next unit of dynamically dealt work (MoE stream kernel); zero between kernels
+    int status;               // 0 or the code of the wait that gave up; sticky until the workspace is initialised again
     unsigned int ticket;      // CTAs that have left the kernel (see barrier_finish)
-    unsigned int reserved[12];
+    unsigned int epoch;       // kernels that have finished on this workspace; tags the words of the mailboxes
+    unsigned int reserved[11];
     // %globaltimer stamps (ns) written by CTA 0 of the last kernel that used this workspace, one
     // per phase boundary; read back with mk36_workspace_trace
     unsigned long long trace[kTraceSlots];
@@ -100,9 +104,20 @@ struct Control {
 // CTA c writes slot s at kCtaTraceOffset + (c * kCtaTraceSlots + s) * 8 (read back with
 // mk36_workspace_cta_trace; used to see how far apart the CTAs reach a phase boundary).
 constexpr size_t kCtaTraceOffset = 4096;
-constexpr int kCtaTraceSlots = 4;
-constexpr int kCtaTraceMaxCtas = 384;
-constexpr size_t kControlBytes = 16384;
+constexpr int kCtaTraceSlots = 8;
+constexpr int kCtaTraceMaxCtas = 192;
+// Mailboxes: 64-bit words {value, tag} that carry small results from every CTA to every CTA without a
+// barrier.  Every receiving CTA has its own copy (kTagSlots words), so no line is polled by more than one
+// CTA.  A word is valid for the running kernel when its tag is Control::epoch + 1; the epoch grows by one
+// per finished kernel, so the words never need clearing.  The mailboxes sit at a fixed offset of the
+// workspace that no kernel uses as scratch and mk36_workspace_init zeroes, so a stale bit pattern can
+// never pass for a tag.  (MoE stream kernel: router logits.)
+constexpr int kTagSlots = 512;
+constexpr int kMailboxMaxCtas = 256;
+constexpr size_t kMailboxOffset = size_t(16) << 20;
+constexpr size_t kMailboxBytes = (size_t)kMailboxMaxCtas * kTagSlots * 8;
+constexpr size_t kTaggedEnd = kMailboxOffset + kMailboxBytes;
+constexpr size_t kControlBytes = 32768;
 static_assert(sizeof(Control) <= kCtaTraceOffset, "control block too large");
 static_assert(kCtaTraceOffset + (size_t)kCtaTraceMaxCtas * kCtaTraceSlots * 8 <= kControlBytes, "per-CTA trace does not fit");
 
@@ -111,6 +126,7 @@ constexpr int kStatusMoeBarrier1 = 101;
 constexpr int kStatusMoeBarrier2 = 102;
 constexpr int kStatusMoeRingProducer = 111;  // producer warp: a stage was never released
 constexpr int kStatusMoeRingConsumer = 112;  // consumer warp: a stage never filled
+constexpr int kStatusMoeLogits = 121;        // stream kernel: another CTA's router logits never arrived
 constexpr int kStatusDenseBarrier = 201;
 constexpr int kStatusAttnBarrier = 301;
 constexpr int kStatusSelfTest = 901;
@@ -177,10 +193,23 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     return v;
 }
 
-// Returns false when the wait ran out; the status word then holds `code`.
+__device__ __forceinline__ int ld_volatile_s32(const int* p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// Returns false when the wait ran out; the status word then holds `code`.  A status word that is
+// already set makes every wait fail at once: after a wait has given up the counters are left dirty
+// (the CTAs that gave up never reach barrier_finish), so nothing may compute on this workspace
+// until the host has initialised it again, and the kernels queued behind the failure leave their
+// outputs untouched.
 __device__ __forceinline__ bool barrier_wait(Control* c, unsigned target, int code,
                                              unsigned long long limit_ns = kWaitLimitNs) {
-    if (ld_acquire_u32(&c->bar_count) >= target) return true;
+    const int dirty = ld_volatile_s32(&c->status);  // issued before the acquire load: both are in flight together
+    const unsigned seen = ld_acquire_u32(&c->bar_count);
+    if (dirty != 0) return false;
+    if (seen >= target) return true;
     const unsigned long long t0 = global_timer_ns();
     unsigned spins = 0;
     while (ld_acquire_u32(&c->bar_count) < target) {
@@ -200,7 +229,9 @@ __device__ __forceinline__ bool barrier_wait(Control* c, unsigned target, int co
 __device__ __forceinline__ void barrier_finish(Control* c, unsigned nblocks) {
     if (atomicAdd(&c->ticket, 1u) == nblocks - 1u) {
         c->bar_count = 0u;
+        c->work_ticket = 0u;
         c->ticket = 0u;
+        c->epoch = c->epoch + 1u;
         __threadfence();
     }
 }

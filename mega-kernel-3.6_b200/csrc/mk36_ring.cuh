@@ -56,7 +56,7 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 // Bounded wait for the phase with the given parity.  `abort_flag` is a shared-memory word that
 // any warp of the CTA sets when it gives up.  The spinning part is kept out of line: these
 // kernels run every code path about once per launch, so their time is sensitive to code size.
-__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
+static __device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                            unsigned long long limit_ns) {
     const unsigned long long t0 = global_timer_ns();
     unsigned spins = 0;

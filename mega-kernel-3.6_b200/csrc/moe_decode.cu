@@ -646,6 +646,8 @@ const void* moe_kernel(int dtype, int tb) {
 
 int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                            bool* handled);
+int moe_decode_stream_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                             bool* handled);
 
 // `comm` (may be null) makes the kernels end with the cross-GPU sum of the ranks' partial outputs.
 int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -655,6 +657,10 @@ int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* works
         MK36_FAIL(MK36_ERR_INVALID_ARG, "moe_decode: the multi-GPU entry points write `out` and take no partial_out");
     if (!options().force_generic) {
         bool handled = false;
+        if (options().moe_stream && !options().ring_mma) {
+            rc = moe_decode_stream_launch(a, comm, workspace, workspace_bytes, stream, &handled);
+            if (rc != MK36_OK || handled) return rc;
+        }
         rc = moe_decode_ring_launch(a, comm, workspace, workspace_bytes, stream, &handled);
         if (rc != MK36_OK || handled) return rc;
     }
@@ -741,7 +747,10 @@ size_t mk36_moe_workspace_bytes(const mk36_moe_args* a) {
     if (!a) return 0;
     MoePlan plan;
     if (!plan_moe(*a, 227 * 1024, &plan)) return 0;
-    return kControlBytes + plan.scratch_bytes;
+    size_t need = kControlBytes + plan.scratch_bytes;
+    // launches of one or two tokens of a 2-byte dtype use the stream kernel when the workspace also holds its mailboxes
+    if (a->dtype != MK36_F32 && a->batch <= 2 && need < kTaggedEnd) need = kTaggedEnd;
+    return need;
 }
 
 int mk36_moe_decode(const mk36_moe_args* args, void* workspace, size_t workspace_bytes, void* stream) {

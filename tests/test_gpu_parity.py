@@ -94,6 +94,30 @@ def test_moe_ring_kernel_tensor_core_consumers_match_oracle(name, cuda_device):
     assert_output_parity(got["out"], ref["out"], what=name + " (tensor-core consumers)")
 
 
+@pytest.mark.parametrize("name", ["moe_small_f16_b2", "moe_35b_bf16_b1_s0", "moe_35b_bf16_b2_s0"])
+@pytest.mark.parametrize("option", ["moe_stream=0", "moe_static=1", "moe_stages=3"])
+def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device):
+    """Calls of one or two tokens run the stream kernel; the same calls through the ring kernel's
+    plain-FMA consumers, and the stream kernel with statically dealt chunks or a shallower ring,
+    must meet the same tolerances."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    key, value = option.split("=")
+    default = {"moe_stream": 1, "moe_static": 0, "moe_stages": 0}[key]
+    cabi.check(lib.mk36_set_option(key.encode(), int(value)))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(key.encode(), default))
+    ref = run_oracle(case, spec)
+    assert_indices_exact(got["indices"], ref["indices"])
+    torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+    assert_output_parity(got["out"], ref["out"], what=f"{name} ({option})")
+
+
 @pytest.mark.parametrize("name", ["attn_27b_bf16_t1000", "attn_35b_bf16_t4096", "attn_35b_bf16_b2_t2500"])
 def test_attention_general_kernel_matches_oracle(name, cuda_device):
     """Shapes that normally take the tensor-core attention kernel, forced through the general one."""
