@@ -243,15 +243,26 @@ MK36_API int mk36_full_attention_decode(const mk36_attention_args* args, void* w
  * MK36_STATIC_SCRATCH_BYTES device array inside the library, and the call performs no device
  * allocation of any kind.
  *   - A problem whose launch plan needs more scratch than the array holds fails with
- *     MK36_ERR_WORKSPACE and a message that names the limit (on a 148-SM part every supported
- *     shape, head_dim <= 256, needs less than 1.3 MB).
+ *     MK36_ERR_WORKSPACE and a message that names the limit, before anything is launched (`out` is
+ *     left untouched).  With bf16 / f16 inputs, head_dim 64 / 128 / 256 and up to 8 query heads per KV
+ *     head (the tensor-core kernel, one CTA per SM) the need stays below 1.3 MB on a 148-SM part; other
+ *     dtypes and head sizes take the general kernel, whose need grows with its occupancy and can
+ *     exceed the array.
  *   - All calls on one GPU share the array.  Each call clears the control block on `stream` before
  *     its kernels; calls that may overlap on the same GPU (other streams or host threads) race on
  *     the array and their results are undefined - serialise them.
  *   - The first call on each GPU also looks up the array's device address; make that first call
- *     outside of any stream capture. */
+ *     outside of any stream capture.
+ *   - The bounded device-side wait of the attention kernels records a give-up in a status word that
+ *     lives in the array.  mk36_static_scratch_status synchronises `stream` and returns that word in
+ *     *device_status (0 = clean; otherwise the code, and MK36_ERR_BARRIER_TIMEOUT as the return
+ *     value); call it before the next static call on the GPU, which clears the word.  A call whose
+ *     status is not 0 may have left `out` partly unwritten.
+ * mk36_set_option("static_scratch_limit", n) makes the entry point treat its array as n bytes
+ * (0 = the full size), so that the refusal can be tried with a small problem. */
 #define MK36_STATIC_SCRATCH_BYTES (2u << 20)
 MK36_API int mk36_full_attention_decode_static(const mk36_attention_args* args, void* stream);
+MK36_API int mk36_static_scratch_status(void* stream, int* device_status);
 
 /* ---------------------------------------------------------------------------------------------
  * Linear-attention recurrent decode step with an fp32 state:

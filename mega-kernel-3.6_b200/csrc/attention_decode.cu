@@ -226,6 +226,7 @@ int attention_decode_launch(const mk36_attention_args* a, void* workspace, size_
     if (batch_per_launch > a->batch) batch_per_launch = a->batch;
 
     const size_t es = a->dtype == MK36_F32 ? 4 : 2;
+    // every launch of the call must fit before the first one is made: a refused call writes nothing
     for (int b0 = 0; b0 < a->batch; b0 += batch_per_launch) {
         mk36_attention_args sub = *a;
         sub.batch = (a->batch - b0 < batch_per_launch) ? (a->batch - b0) : batch_per_launch;
@@ -234,6 +235,12 @@ int attention_decode_launch(const mk36_attention_args* a, void* workspace, size_
         if (workspace_bytes < kControlBytes + plan.scratch_bytes)
             MK36_FAIL(MK36_ERR_WORKSPACE, "full_attention_decode: workspace too small (%zu < %zu bytes)", workspace_bytes,
                       kControlBytes + plan.scratch_bytes);
+    }
+    for (int b0 = 0; b0 < a->batch; b0 += batch_per_launch) {
+        mk36_attention_args sub = *a;
+        sub.batch = (a->batch - b0 < batch_per_launch) ? (a->batch - b0) : batch_per_launch;
+        AttnPlan plan;
+        plan_generic(sub, (int)max_ctas, &plan);
         AttnParams p;
         p.q = static_cast<const unsigned char*>(a->q) + (size_t)b0 * a->query_heads * a->head_dim * es;
         p.k = static_cast<const unsigned char*>(a->k_cache) + (size_t)b0 * a->seq_len * a->kv_heads * a->head_dim * es;

@@ -18,7 +18,7 @@
 // Online soft-max state is per warp; warps are folded in shared memory, splits through the shared
 // merge (one bounded grid barrier).  Arithmetic follows mega_kernel_qwen36/reference.py:117-145
 // (fp32 scores and accumulation); the probabilities enter the second product rounded to the
-// storage dtype, which is averaged out over the context and stays far inside the tolerance.
+// storage dtype and the normaliser is summed from the same rounded values.
 #include <cfloat>
 
 #include "mk36_attention.cuh"
@@ -57,6 +57,17 @@ template <>
 __device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <typename T>
+__device__ __forceinline__ float2 unpack2(unsigned v);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(unsigned v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(unsigned v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
 __device__ __forceinline__ unsigned transpose8x8(unsigned v) {
@@ -177,8 +188,13 @@ __global__ void __launch_bounds__(kMmaAttnThreads, 1) attention_decode_mma_kerne
         const float c0 = (mrun[0] == -INFINITY) ? 0.0f : __expf(mrun[0] - mn0);
         const float c1 = (mrun[1] == -INFINITY) ? 0.0f : __expf(mrun[1] - mn1);
         const float p0 = __expf(s[0] - mn0), p1 = __expf(s[1] - mn1), p2 = __expf(s[2] - mn0), p3 = __expf(s[3] - mn1);
-        lrun[0] = lrun[0] * c0 + p0 + p2;
-        lrun[1] = lrun[1] * c1 + p1 + p3;
+        // The probabilities enter the second product rounded to the storage dtype; the normaliser is summed
+        // from the same rounded values, so that the output weights still add up to one (with the unrounded
+        // sum a short context, where nothing averages out, would carry the rounding error of each weight).
+        const unsigned pk01 = pack2<T>(p0, p1), pk23 = pack2<T>(p2, p3);
+        const float2 r01 = unpack2<T>(pk01), r23 = unpack2<T>(pk23);
+        lrun[0] = lrun[0] * c0 + r01.x + r23.x;
+        lrun[1] = lrun[1] * c1 + r01.y + r23.y;
         if (__any_sync(kFullMask, (mn0 != mrun[0]) || (mn1 != mrun[1]))) {
 #pragma unroll
             for (int m = 0; m < NW; ++m) {
@@ -188,8 +204,8 @@ __global__ void __launch_bounds__(kMmaAttnThreads, 1) attention_decode_mma_kerne
         mrun[0] = mn0;
         mrun[1] = mn1;
         // probabilities as the B operand: (tokens 2t,2t+1 | 2t+8,2t+9 ; head g)
-        const unsigned b0 = transpose8x8(pack2<T>(p0, p1));
-        const unsigned b1 = transpose8x8(pack2<T>(p2, p3));
+        const unsigned b0 = transpose8x8(pk01);
+        const unsigned b1 = transpose8x8(pk23);
 
         // ---- output: word m of a token holds channels g*D/8 + 2m, 2m+1 ----
 #pragma unroll
@@ -313,17 +329,28 @@ int attention_decode_mma_launch(const mk36_attention_args* a, void* workspace, s
         MK36_FAIL(MK36_ERR_WORKSPACE, "full_attention_decode: workspace is NULL or not 256-byte aligned");
 
     const size_t es = 2;
-    for (int b0 = 0; b0 < a->batch; b0 += batch_per_launch) {
-        const int nb = (a->batch - b0 < batch_per_launch) ? (a->batch - b0) : batch_per_launch;
+    auto splits_for = [&](int nb) {
         long long splits = max_ctas / ((long long)nb * a->kv_heads);
         const long long by_len = (a->seq_len + 8 * kTileTokens - 1) / (8 * kTileTokens);  // at least one tile per warp
         if (splits > by_len) splits = by_len;
-        if (splits < 1) splits = 1;
+        return splits < 1 ? 1ll : splits;
+    };
+    auto scratch_for = [&](int nb, long long splits) {
         const size_t heads = (size_t)nb * a->query_heads;
-        const size_t scratch = align_up(heads * splits * D * 4, 256) + 2 * align_up(heads * splits * 4, 256);
+        return align_up(heads * splits * D * 4, 256) + 2 * align_up(heads * splits * 4, 256);
+    };
+    // every launch of the call must fit before the first one is made: a refused call writes nothing
+    for (int b0 = 0; b0 < a->batch; b0 += batch_per_launch) {
+        const int nb = (a->batch - b0 < batch_per_launch) ? (a->batch - b0) : batch_per_launch;
+        const size_t scratch = scratch_for(nb, splits_for(nb));
         if (workspace_bytes < kControlBytes + scratch)
             MK36_FAIL(MK36_ERR_WORKSPACE, "full_attention_decode: workspace too small (%zu < %zu bytes)", workspace_bytes,
                       kControlBytes + scratch);
+    }
+    for (int b0 = 0; b0 < a->batch; b0 += batch_per_launch) {
+        const int nb = (a->batch - b0 < batch_per_launch) ? (a->batch - b0) : batch_per_launch;
+        const long long splits = splits_for(nb);
+        const size_t heads = (size_t)nb * a->query_heads;
         AttnParams p;
         p.q = static_cast<const unsigned char*>(a->q) + (size_t)b0 * a->query_heads * D * es;
         p.k = static_cast<const unsigned char*>(a->k_cache) + (size_t)b0 * a->seq_len * a->kv_heads * D * es;

@@ -163,6 +163,10 @@ int mk36_set_option(const char* name, int value) {
         options().moe_stages = value > 0 ? value : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "static_scratch_limit") == 0) {
+        options().static_scratch_limit = value > 0 ? value : 0;
+        return MK36_OK;
+    }
     if (std::strcmp(name, "moe_static") == 0) {
         options().moe_static = value ? 1 : 0;
         return MK36_OK;

@@ -114,6 +114,9 @@ __device__ __forceinline__ bool comm_get_sum(const CommParams& c, Control* ctl, 
         unsigned long long w;
         asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(addr) : "memory");
         if ((unsigned)(w >> 32) != step + 1u) {
+            // once any wait of this kernel has given up the others do not start theirs: the kernel ends within
+            // one wait limit, not one per element
+            if (ld_volatile_s32(&ctl->status) != 0) return false;
             if (!comm_poll_slow(addr, step + 1u, ctl, &w)) return false;
         }
         v += __uint_as_float((unsigned)w);

@@ -97,6 +97,7 @@ SIGNATURES = {
     "mk36_attention_workspace_bytes": (C.c_size_t, [C.POINTER(AttentionArgs)]),
     "mk36_full_attention_decode": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_full_attention_decode_static": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),
+    "mk36_static_scratch_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "mk36_linear_attention_decode": (C.c_int, [C.POINTER(LinearAttentionArgs), C.c_void_p]),
     "mk36_linear_attention_decode_steps": (C.c_int, [C.POINTER(LinearAttentionStepsArgs), C.c_void_p]),
     "mk36_comm_buffer_bytes": (C.c_size_t, []),

@@ -167,6 +167,8 @@ class KernelLaunch:
     phases: Tuple[KernelPhase, ...] = ()
     hbm_bytes: int = 0                   # distinct bytes that must cross HBM once
     layer: Optional[int] = None
+    kernel: Optional[str] = None         # the __global__ function that runs
+    launches: int = 1                    # launches of that kernel per decode step (a batch may be split)
 
     def to_dict(self) -> Dict[str, Any]:
         d = dict(self.__dict__)
@@ -443,6 +445,39 @@ def build_qwen36_decode_tgraph(
 # ---------------------------------------------------------------------------------------------
 # B200 kernel schedule
 # ---------------------------------------------------------------------------------------------
+# Launch geometry of the kernels in csrc/: threads per CTA, grid-wide barriers per launch.  The numbers
+# mirror the constants of the .cu files (kStThreads, kRingThreads, kDenseThreads, kMmaAttnThreads,
+# kLinThreads); tests/test_host_api.py reads those files and fails when the two drift apart.
+KERNEL_GEOMETRY = {
+    "moe_decode_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 2},
+    "moe_decode_ring_kernel": {"block": 416, "grid_barriers": 2, "max_tokens": 8},
+    "dense_ffn_mma_kernel": {"block": 512, "grid_barriers": 1, "max_tokens": 8},
+    "attention_decode_mma_kernel": {"block": 256, "grid_barriers": 1},
+    "linear_attention_kernel": {"block": 256, "grid_barriers": 0},
+}
+_SMEM_OPTIN = 232448   # bytes of shared memory one CTA may use on sm_100
+_RING_STAGE = 32768
+
+
+def moe_ring_tokens_per_launch(hidden: int, top_k: int, intermediate: int, shared_intermediate: int, sms: int = 148) -> int:
+    """Tokens the MoE ring kernel serves in one launch: the largest power of two <= 8 whose per-pair
+    activations (fp32, or bf16 high + low halves) leave room for three 32 KB ring stages beside them -
+    the same fit loop as the launcher in csrc/moe_decode_ring.cu."""
+    hr_max = -(-hidden // sms)
+    tb = 8
+    while tb > 1 and tb * top_k > 64:
+        tb //= 2
+    while tb >= 1:
+        pairs = tb * top_k
+        used = hr_max * shared_intermediate * 2
+        used += max(tb * hidden * 2, (pairs * intermediate + tb * shared_intermediate) * 4)
+        used += (pairs + tb) * hr_max * 4 + 3 * 2 * 4 * 128 * 4 + 16 + 64 * (4 + 8 + 4 + 4) + (2 * 6 + 1 + 4) * 8 + 6 * 128
+        if (_SMEM_OPTIN - used - 1024) // _RING_STAGE >= 3:
+            return tb
+        tb //= 2
+    return 1
+
+
 def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len: int = 32768) -> Tuple[KernelLaunch, ...]:
     """Groups the graph's tasks into the launches libmk36 performs.  The byte counts are the
     distinct bytes each launch must read or write in HBM (bf16 weights and cache, fp32 state); for
@@ -466,7 +501,8 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             row = hkv * hd * 2
             launches.append(KernelLaunch(
                 name=f"layer_{li}_attention", entry_point="mk36_full_attention_decode", task_ids=(task.id,),
-                grid=sms, block=256, grid_barriers=1, layer=li,
+                kernel="attention_decode_mma_kernel", grid=sms, block=KERNEL_GEOMETRY["attention_decode_mma_kernel"]["block"],
+                grid_barriers=KERNEL_GEOMETRY["attention_decode_mma_kernel"]["grid_barriers"], layer=li,
                 phases=(KernelPhase("split_kv_online_softmax", 2 * batch * context_len, row, "runtime"),
                         KernelPhase("merge_partials", 0, 0, "static")),
                 hbm_bytes=batch * (2 * context_len * row + 2 * hq * hd * 2)))
@@ -475,7 +511,8 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
             launches.append(KernelLaunch(
                 name=f"layer_{li}_linear_attention", entry_point="mk36_linear_attention_decode", task_ids=(task.id,),
-                grid=batch * hv * _ceil_div(dv, 32), block=256, grid_barriers=0, layer=li,
+                kernel="linear_attention_kernel", grid=batch * hv * _ceil_div(dv, 32),
+                block=KERNEL_GEOMETRY["linear_attention_kernel"]["block"], grid_barriers=0, layer=li,
                 phases=(KernelPhase("state_update_and_readout", batch * hv * dk, dv * 4 * 2, "static"),),
                 hbm_bytes=2 * batch * hv * dk * dv * 4 + batch * (2 * hk * dk + 2 * hv * dv) * 2))
         elif task.kind == "rmsnorm" and task.attrs.get("ffn"):
@@ -487,9 +524,16 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             E, K = cfg.num_experts, cfg.num_experts_per_tok
             I, Is = cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
             distinct = min(batch * K, E)
+            # one or two tokens: the stream kernel; more: the ring kernel, as many tokens per launch as fit
+            if batch <= KERNEL_GEOMETRY["moe_decode_stream_kernel"]["max_tokens"]:
+                kname, n_launches = "moe_decode_stream_kernel", 1
+            else:
+                kname = "moe_decode_ring_kernel"
+                n_launches = _ceil_div(batch, moe_ring_tokens_per_launch(H, K, I, Is, sms))
+            geo = KERNEL_GEOMETRY[kname]
             launches.append(KernelLaunch(
                 name=f"layer_{li}_moe", entry_point="mk36_moe_decode", task_ids=tuple(t.id for t in group),
-                grid=sms, block=512, grid_barriers=2, layer=li,
+                kernel=kname, launches=n_launches, grid=sms, block=geo["block"], grid_barriers=geo["grid_barriers"], layer=li,
                 phases=(KernelPhase("rmsnorm_to_smem", 0, 0, "static"),
                         KernelPhase("router_logits", E, H * 2, "static"),
                         KernelPhase("shared_gate_up", 2 * Is, H * 2, "static"),
@@ -502,7 +546,9 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             I = cfg.intermediate_size
             launches.append(KernelLaunch(
                 name=f"layer_{li}_dense_ffn", entry_point="mk36_dense_ffn_decode", task_ids=tuple(t.id for t in group),
-                grid=sms, block=512, grid_barriers=1, layer=li,
+                kernel="dense_ffn_mma_kernel", launches=_ceil_div(batch, KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["max_tokens"]),
+                grid=sms, block=KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["block"],
+                grid_barriers=KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["grid_barriers"], layer=li,
                 phases=(KernelPhase("rmsnorm_to_smem", 0, 0, "static"),
                         KernelPhase("gate_up_swiglu", 2 * I, H * 2, "static"),
                         KernelPhase("down_and_residual", H, I * 2, "static")),

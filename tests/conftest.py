@@ -19,6 +19,24 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200) and the built sm_100a extension")
 
 
+def pytest_sessionfinish(session, exitstatus):
+    """Writes the parity figures of the session (plain max-abs, relative L2 and the number of elements
+    beyond a flat 2e-2 per comparison) to the file named by MK36_PARITY_REPORT, when that is set."""
+    import json
+    import os
+
+    target = os.environ.get("MK36_PARITY_REPORT")
+    if not target:
+        return
+    try:
+        import parity
+
+        if parity.REPORT:
+            Path(target).write_text(json.dumps(parity.REPORT, indent=1, sort_keys=True))
+    except Exception:  # a report is a convenience, never a reason to fail the session
+        pass
+
+
 @pytest.fixture(scope="session")
 def cuda_device():
     import torch

@@ -87,7 +87,7 @@ def run_case(ref, case) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of the reference project")
     ap.add_argument("--only", nargs="*", default=None)
     ns = ap.parse_args()
     ref = load_reference(Path(ns.reference))

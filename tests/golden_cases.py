@@ -64,8 +64,12 @@ CASES = [
     Case("moe_35b_bf16_b4_s0", "moe", _moe(syn.MOE_35B_A3B, 4, 0, BF16), heavy=True),
     Case("moe_35b_bf16_b8_s0", "moe", _moe(syn.MOE_35B_A3B, 8, 0, BF16), heavy=True),
     Case("moe_35b_bf16_b1_s1", "moe", _moe(syn.MOE_35B_A3B, 1, 1, BF16), heavy=True),
+    Case("moe_35b_bf16_b2_s1", "moe", _moe(syn.MOE_35B_A3B, 2, 1, BF16), heavy=True),
+    Case("moe_35b_bf16_b4_s1", "moe", _moe(syn.MOE_35B_A3B, 4, 1, BF16), heavy=True),
     Case("moe_35b_bf16_b8_s1", "moe", _moe(syn.MOE_35B_A3B, 8, 1, BF16), heavy=True),
     Case("moe_35b_bf16_b1_s2", "moe", _moe(syn.MOE_35B_A3B, 1, 2, BF16), heavy=True),
+    Case("moe_35b_bf16_b2_s2", "moe", _moe(syn.MOE_35B_A3B, 2, 2, BF16), heavy=True),
+    Case("moe_35b_bf16_b4_s2", "moe", _moe(syn.MOE_35B_A3B, 4, 2, BF16), heavy=True),
     Case("moe_35b_bf16_b8_s2", "moe", _moe(syn.MOE_35B_A3B, 8, 2, BF16), heavy=True),
     # --- dense FFN -------------------------------------------------------------------------
     Case("dense_tiny_f32_b2", "dense", _dense(syn.DENSE_TINY, 2, 23, F32, x_std=0.08, w_std=0.08, norm_jitter=0.08)),

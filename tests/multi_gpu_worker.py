@@ -2,7 +2,7 @@
 
 Every rank builds the same seeded full weights on the host, keeps its shard on its GPU, and runs
 the expert-parallel MoE / tensor-parallel dense FFN with the cross-GPU sum fused into the kernel
-(`PeerExchange`).  Checked on every rank: the result against the CPU oracle on the full weights
+(`PeerExchange`), and the KV-head-parallel attention where the head count divides by the world size.  Checked on every rank: the result against the CPU oracle on the full weights
 (the tolerances of tests/parity.py), routing bit-exact, the NCCL all-reduce variant within the
 same tolerance, several steps in a row (both halves of the double-buffered exchange), and - on
 rank 0 - that all ranks hold bit-identical outputs.
@@ -57,6 +57,7 @@ def main() -> int:
             ("moe_small_bf16", syn.MOE_SMALL, 3, torch.bfloat16, 4),
             ("moe_small_f32", syn.MOE_SMALL, 2, torch.float32, 4),
             ("moe_35b_b1", syn.MOE_35B_A3B, 1, torch.bfloat16, 8),
+            ("moe_35b_b2", syn.MOE_35B_A3B, 2, torch.bfloat16, 8),
             ("moe_35b_b8", syn.MOE_35B_A3B, 8, torch.bfloat16, 8),
         ]
         for name, shape, batch, dtype, top_k in moe_cases:
@@ -117,6 +118,19 @@ def main() -> int:
                 same_on_all_ranks(out, f"{name} step {step}")
             del local, host, full, cut
             torch.cuda.empty_cache()
+        # ---------------- attention, KV-head parallel (no exchange; only where the head count allows) ----------------
+        for name, heads, kv_heads, dim, seq in (("attn_35b_t2048", 16, 2, 256, 2048), ("attn_27b_t1000", 24, 4, 256, 1000)):
+            if kv_heads % world != 0:
+                continue
+            t = syn.attention_tensors(1, heads, kv_heads, dim, seq, seed=11)
+            scale = 1.0 / float(dim) ** 0.5
+            full = mk.FullAttentionInputs(q=t["q"], k_cache=t["k_cache"], v_cache=t["v_cache"], scale=scale)
+            cut = parallel.shard_attention_inputs(full, rank, world)
+            mine = mk.FullAttentionInputs(q=cut.q.to(device), k_cache=cut.k_cache.to(device), v_cache=cut.v_cache.to(device), scale=cut.scale)
+            out = parallel.full_attention_decode_kvp(mine, gather=True)
+            ro = oracle.full_attention_decode(t["q"], t["k_cache"], t["v_cache"], scale=scale)
+            check(parity.assert_output_parity, out.cpu(), ro, f"{name} kv-head parallel")
+            same_on_all_ranks(out, name)
     except AssertionError as exc:  # keep the ranks in step: report, do not leave peers waiting
         failures.append(f"rank {rank}: {exc}")
     torch.cuda.synchronize()

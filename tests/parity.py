@@ -9,6 +9,12 @@ magnitude >= 4 has a spacing of 2^-5 = 0.031 or more, so two correct fp32 result
 the last bit but straddle a rounding boundary already differ by more than 2e-2 after rounding.
 The per-element bound is therefore max(2e-2, one unit in the last place of the oracle's value in
 the output dtype); for |value| < 4 in bf16 this is exactly 2e-2.
+
+The refinement is kept honest in numbers: every comparison records the plain max-abs and how many
+elements differ by more than a flat 2e-2 (each of them by exactly one rounding step of a value of
+magnitude >= 4), and fails when that count exceeds ROUNDING_FLIPS_ALLOWED per thousand elements
+(at least ROUNDING_FLIPS_MIN).  `REPORT` collects the figures of a test session; tests/conftest.py
+writes them to a JSON file when the session ends.
 """
 
 from __future__ import annotations
@@ -18,6 +24,10 @@ import torch
 MAX_ABS = 2e-2
 REL_L2 = 1e-2
 STATE_REL = 1e-4
+ROUNDING_FLIPS_ALLOWED = 2   # per thousand elements
+ROUNDING_FLIPS_MIN = 4
+
+REPORT = {}  # what -> {"max_abs", "rel_l2", "over_2e-2", "elements"} of every output comparison of the session
 
 
 def _ulp(ref: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -50,9 +60,14 @@ def assert_output_parity(actual: torch.Tensor, expected: torch.Tensor, what: str
     diff = (a - e).abs()
     worst = float((diff - bound).max())
     r = rel_l2(a, e)
+    flips = int((diff > max_abs_tol).sum()) if max_abs_tol > 0 else 0
+    allowed = max(ROUNDING_FLIPS_MIN, ROUNDING_FLIPS_ALLOWED * a.numel() // 1000)
+    result = {"max_abs": float(diff.max()), "rel_l2": r, "over_2e-2": flips, "elements": int(a.numel())}
+    REPORT[what] = result
     assert worst <= 0.0, f"{what}: max-abs {float(diff.max()):.4g} exceeds bound (worst excess {worst:.3g})"
     assert r <= rel_l2_tol, f"{what}: rel-L2 {r:.4g} > {rel_l2_tol}"
-    return {"max_abs": float(diff.max()), "rel_l2": r}
+    assert flips <= allowed, f"{what}: {flips} elements differ by more than {max_abs_tol} (one bf16 rounding step each); {allowed} allowed"
+    return result
 
 
 def assert_oracle_matches_fixture(actual: torch.Tensor, fixture: torch.Tensor, what: str) -> None:

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import mega_kernel_qwen36 as mk
-from mega_kernel_qwen36 import cabi, synthetic as syn
+from mega_kernel_qwen36 import cabi, mpk_graph, synthetic as syn
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -81,7 +81,8 @@ def test_b200_worker_defaults_and_kernel_schedule():
     plan = mk.build_qwen36_decode_tgraph(cfg, batch_size=1, num_layers=4, worker_config=wc).linearize(wc, batch_size=1)
     launches = {k.name: k for k in plan.kernel_schedule}
     moe = launches["layer_0_moe"]
-    assert moe.entry_point == "mk36_moe_decode" and moe.grid == 148 and moe.grid_barriers == 2
+    assert moe.entry_point == "mk36_moe_decode" and moe.grid == 148
+    assert (moe.kernel, moe.block, moe.grid_barriers, moe.launches) == ("moe_decode_stream_kernel", 416, 1, 1)
     assert moe.task_ids == ("layer_0_ffn_norm", "layer_0_moe_router_topk", "layer_0_moe_grouped_experts", "layer_0_moe_down_residual")
     assert moe.hbm_bytes == syn.moe_algorithmic_bytes(syn.MOE_35B_A3B, 1, 8) == 57_684_064
     attn = launches["layer_3_attention"]
@@ -96,6 +97,44 @@ def test_b200_worker_defaults_and_kernel_schedule():
     assert dense.hbm_bytes == syn.dense_algorithmic_bytes(syn.DENSE_27B, 8) == 534_947_840
     data = json.loads(plan.to_json())
     assert data["worker_config"]["total_sms"] == 148 and len(data["kernel_schedule"]) == len(plan.kernel_schedule)
+    # eight tokens: the ring kernel, split into launches of as many tokens as its shared memory holds
+    plan8 = mk.build_qwen36_decode_tgraph(cfg, batch_size=8, num_layers=1, worker_config=wc).linearize(wc, batch_size=8)
+    moe8 = {k.name: k for k in plan8.kernel_schedule}["layer_0_moe"]
+    assert (moe8.kernel, moe8.block, moe8.grid_barriers) == ("moe_decode_ring_kernel", 416, 2)
+    assert moe8.launches == -(-8 // mpk_graph.moe_ring_tokens_per_launch(2048, 8, 512, 512))
+
+
+def test_kernel_geometry_table_matches_the_cuda_sources():
+    """The planner's launch geometry is a mirror of constants in csrc/; read them there."""
+    import re
+
+    csrc = Path(mk.__file__).resolve().parent.parent / "csrc"
+
+    def constants(name):
+        text = (csrc / name).read_text()
+        found = {}
+        for m in re.finditer(r"constexpr int (k\w+) = ([^;]+);", text):
+            expr = m.group(2).split("//")[0].strip()
+            try:
+                found[m.group(1)] = int(eval(expr, {}, dict(found)))
+            except Exception:
+                pass
+        return found
+
+    geo = mpk_graph.KERNEL_GEOMETRY
+    st = constants("moe_decode_stream.cu")
+    assert geo["moe_decode_stream_kernel"]["block"] == st["kStThreads"]
+    assert geo["moe_decode_stream_kernel"]["max_tokens"] == st["kStMaxTokens"]
+    ring = constants("moe_decode_ring.cu")
+    assert geo["moe_decode_ring_kernel"]["block"] == ring["kRingThreads"]
+    assert geo["moe_decode_ring_kernel"]["max_tokens"] == ring["kRingMaxTokens"]
+    assert mpk_graph._RING_STAGE == ring["kRingStageBytes"]
+    assert geo["dense_ffn_mma_kernel"]["block"] == constants("dense_ffn_mma.cu")["kDenseThreads"]
+    assert geo["attention_decode_mma_kernel"]["block"] == constants("attention_decode_mma.cu")["kMmaAttnThreads"]
+    assert geo["linear_attention_kernel"]["block"] == constants("linear_attention_decode.cu")["kLinThreads"]
+    # the grid barriers: one barrier_arrive per barrier in the kernel's source
+    assert (csrc / "moe_decode_stream.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_stream_kernel"]["grid_barriers"]
+    assert (csrc / "moe_decode_ring.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_ring_kernel"]["grid_barriers"]
 
 
 def test_graph_rejects_duplicates_and_cycles():

@@ -108,3 +108,51 @@ def test_static_scratch_entry_argument_errors(cuda_device):
     torch.cuda.synchronize()
     expect = _with_workspace(cabi, lib, t, shape, cabi.MK36_BF16, stream)
     assert torch.equal(out, expect)
+
+
+def test_static_scratch_entry_refuses_what_does_not_fit_and_writes_nothing(cuda_device):
+    """A plan that needs more scratch than the array is refused before anything is launched: the
+    call returns MK36_ERR_WORKSPACE, names the limit, and leaves `out` as it was.  The array is
+    made to look small ("static_scratch_limit") so that a modest problem is enough, once for a
+    single-launch call and once for a batch that would need several launches."""
+    from mega_kernel_qwen36 import cabi
+
+    lib = cabi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    cabi.check(lib.mk36_set_option(b"static_scratch_limit", 48 * 1024))
+    try:
+        for shape in ((1, 16, 2, 256, 4096), (96, 16, 2, 256, 512)):
+            t = _tensors(cuda_device, *shape, seed=31)
+            out = torch.full_like(t["q"], 7.0)
+            rc = lib.mk36_full_attention_decode_static(_args(cabi, t, out, *shape, cabi.MK36_BF16), stream)
+            torch.cuda.synchronize()
+            assert rc == cabi.MK36_ERR_WORKSPACE, (shape, rc)
+            assert b"built-in" in lib.mk36_last_error()
+            assert bool((out == 7.0).all()), f"{shape}: a refused call wrote to out"
+    finally:
+        cabi.check(lib.mk36_set_option(b"static_scratch_limit", 0))
+    # with the full array the first problem fits again and matches the workspace variant
+    shape = (1, 16, 2, 256, 4096)
+    t = _tensors(cuda_device, *shape, seed=31)
+    out = torch.empty_like(t["q"])
+    cabi.check(lib.mk36_full_attention_decode_static(_args(cabi, t, out, *shape, cabi.MK36_BF16), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(out, _with_workspace(cabi, lib, t, shape, cabi.MK36_BF16, stream))
+
+
+def test_static_scratch_status_reads_the_word_in_the_array(cuda_device):
+    """The status word of the static calls lives in the array; the accessor reports it (clean here)."""
+    import ctypes
+
+    from mega_kernel_qwen36 import cabi
+
+    lib = cabi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    shape = (2, 16, 2, 128, 700)
+    t = _tensors(cuda_device, *shape, seed=5)
+    out = torch.empty_like(t["q"])
+    cabi.check(lib.mk36_full_attention_decode_static(_args(cabi, t, out, *shape, cabi.MK36_BF16), stream))
+    status = ctypes.c_int(-1)
+    cabi.check(lib.mk36_static_scratch_status(stream, ctypes.byref(status)))
+    assert status.value == 0
+    assert lib.mk36_static_scratch_status(stream, None) == cabi.MK36_ERR_INVALID_ARG
