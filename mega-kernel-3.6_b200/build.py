@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "moe_decode_stream.cu",
     "dense_ffn_decode.cu",
     "dense_ffn_mma.cu",
+    "dense_ffn_stream.cu",
     "attention_decode.cu",
     "attention_decode_mma.cu",
     "attention_decode_static.cu",

@@ -10,6 +10,8 @@ namespace mk36 {
 int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int dense_ffn_mma_launch(const mk36_dense_ffn_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                          bool* handled);
+int dense_ffn_stream_launch(const mk36_dense_ffn_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                            bool* handled);
 }
 
 using namespace mk36;
@@ -40,11 +42,16 @@ int to_moe_args(const mk36_dense_ffn_args* a, mk36_moe_args* m) {
     return MK36_OK;
 }
 
-// The tensor-core kernel when the shapes suit it, else the shared-expert-only mode of the MoE kernel.
+// One token: the streaming kernel; several: the tensor-core kernel; shapes neither takes: the
+// shared-expert-only mode of the MoE kernel.
 int dense_launch(const mk36_dense_ffn_args* a, const mk36_moe_args* m, const mk36_comm* comm, void* workspace, size_t workspace_bytes,
                  cudaStream_t stream) {
     if (!options().force_generic) {
         bool handled = false;
+        if (options().dense_stream) {
+            const int rc = dense_ffn_stream_launch(a, comm, workspace, workspace_bytes, stream, &handled);
+            if (rc != MK36_OK || handled) return rc;
+        }
         const int rc = dense_ffn_mma_launch(a, comm, workspace, workspace_bytes, stream, &handled);
         if (rc != MK36_OK || handled) return rc;
     }
