@@ -88,8 +88,10 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
  * stream kernel (no grid barrier before the routing, dealt gate/up chunks); "moe_stream" = 0 sends
  * them to the ring kernel instead, "ring_mma" = 1 additionally makes the ring kernel contract with
  * tensor-core instructions whatever the token count.  "moe_stages" (0 = default, else 2..6) sets the
- * stream kernel's ring depth and "moe_static" = 1 makes it deal its chunks without the work counter;
- * both exist for measurements.  Unknown names return MK36_ERR_INVALID_ARG. */
+ * stream kernel's ring depth and "moe_static" = 1 makes it (and the dense streaming kernel) deal
+ * chunks without the work counter; both exist for measurements.  One-token dense FFN calls normally
+ * run the streaming kernel; "dense_stream" = 0 sends them to the tensor-core kernel that serves the
+ * larger batches.  Unknown names return MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 
 /* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase

@@ -118,6 +118,23 @@ def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device)
     assert_output_parity(got["out"], ref["out"], what=f"{name} ({option})")
 
 
+@pytest.mark.parametrize("name", ["dense_mid_f16_b1", "dense_27b_bf16_b1"])
+def test_dense_one_token_through_the_tensor_core_kernel(name, cuda_device):
+    """One-token dense FFN calls run the streaming kernel; the tensor-core kernel that serves larger
+    batches must give the same call the same answer within the tolerances."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    cabi.check(lib.mk36_set_option(b"dense_stream", 0))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(b"dense_stream", 1))
+    assert_output_parity(got["out"], run_oracle(case, spec)["out"], what=name + " (tensor-core kernel)")
+
+
 @pytest.mark.parametrize("name", ["attn_27b_bf16_t1000", "attn_35b_bf16_t4096", "attn_35b_bf16_b2_t2500"])
 def test_attention_general_kernel_matches_oracle(name, cuda_device):
     """Shapes that normally take the tensor-core attention kernel, forced through the general one."""
