@@ -91,7 +91,10 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
  * stream kernel's ring depth and "moe_static" = 1 makes it (and the dense streaming kernel) deal
  * chunks without the work counter; both exist for measurements.  One-token dense FFN calls normally
  * run the streaming kernel; "dense_stream" = 0 sends them to the tensor-core kernel that serves the
- * larger batches.  Unknown names return MK36_ERR_INVALID_ARG. */
+ * larger batches.  Attention calls with bf16 / f16 caches normally run the streaming kernel (cache
+ * chunks of all KV heads through a shared-memory ring); "attn_stream" = 0 sends them to the
+ * tensor-core kernel that stages the cache in registers.  Unknown names return
+ * MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 
 /* Phase trace: CTA 0 of every persistent kernel stamps the GPU's nanosecond timer at its phase
@@ -241,15 +244,17 @@ MK36_API int mk36_full_attention_decode(const mk36_attention_args* args, void* w
  * counterpart in the reference: it exists for hosts that bind the library over a plain C boundary
  * and own no device allocator, or that sit in a request loop where cudaMalloc / cudaFree (which
  * synchronise the device) must not be called.  Same arithmetic, same kernels and same results as
- * mk36_full_attention_decode; the split partials and the barrier control block live in a fixed
+ * mk36_full_attention_decode (bit-identical whenever both pick the same kernel, which they do when the
+ * streaming kernel's partial rows fit the array); the split partials and the barrier control block live in a fixed
  * MK36_STATIC_SCRATCH_BYTES device array inside the library, and the call performs no device
  * allocation of any kind.
  *   - A problem whose launch plan needs more scratch than the array holds fails with
  *     MK36_ERR_WORKSPACE and a message that names the limit, before anything is launched (`out` is
  *     left untouched).  With bf16 / f16 inputs, head_dim 64 / 128 / 256 and up to 8 query heads per KV
- *     head (the tensor-core kernel, one CTA per SM) the need stays below 1.3 MB on a 148-SM part; other
- *     dtypes and head sizes take the general kernel, whose need grows with its occupancy and can
- *     exceed the array.
+ *     head the need is one partial row (head_dim + 2 floats) per query head and SM: 2.5 MB for 16
+ *     heads of 256 on a 148-SM part; when the streaming kernel's rows do not fit, the call takes the
+ *     register-staged tensor-core kernel with half as many rows or fewer.  Other dtypes and head sizes
+ *     take the general kernel, whose need grows with its occupancy and can exceed the array.
  *   - All calls on one GPU share the array.  Each call clears the control block on `stream` before
  *     its kernels; calls that may overlap on the same GPU (other streams or host threads) race on
  *     the array and their results are undefined - serialise them.
@@ -262,7 +267,7 @@ MK36_API int mk36_full_attention_decode(const mk36_attention_args* args, void* w
  *     status is not 0 may have left `out` partly unwritten.
  * mk36_set_option("static_scratch_limit", n) makes the entry point treat its array as n bytes
  * (0 = the full size), so that the refusal can be tried with a small problem. */
-#define MK36_STATIC_SCRATCH_BYTES (2u << 20)
+#define MK36_STATIC_SCRATCH_BYTES (4u << 20)
 MK36_API int mk36_full_attention_decode_static(const mk36_attention_args* args, void* stream);
 MK36_API int mk36_static_scratch_status(void* stream, int* device_status);
 

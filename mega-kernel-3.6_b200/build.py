@@ -38,6 +38,7 @@ CUDA_SOURCES = [
     "dense_ffn_stream.cu",
     "attention_decode.cu",
     "attention_decode_mma.cu",
+    "attention_decode_stream.cu",
     "attention_decode_static.cu",
     "linear_attention_decode.cu",
 ]

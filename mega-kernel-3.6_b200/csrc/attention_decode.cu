@@ -192,12 +192,17 @@ void plan_generic(const mk36_attention_args& a, int max_ctas, AttnPlan* plan) {
 }  // namespace
 
 int attention_decode_mma_launch(const mk36_attention_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled);
+int attention_decode_stream_launch(const mk36_attention_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool* handled);
 
 int attention_decode_launch(const mk36_attention_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int rc = check_attention_args(a);
     if (rc != MK36_OK) return rc;
     if (!options().force_generic) {
         bool handled = false;
+        if (options().attn_stream) {
+            rc = attention_decode_stream_launch(a, workspace, workspace_bytes, stream, &handled);
+            if (rc != MK36_OK || handled) return rc;
+        }
         rc = attention_decode_mma_launch(a, workspace, workspace_bytes, stream, &handled);
         if (rc != MK36_OK || handled) return rc;
     }

@@ -40,9 +40,10 @@ int attention_decode_launch(const mk36_attention_args* a, void* workspace, size_
 namespace {
 
 // Control block + split-KV partials.  A launch holds one partial row (head_dim + 2 floats) per
-// (batch item, query head, split).  The tensor-core kernel runs one CTA per SM, so with bf16 / f16
-// inputs, head_dim 64 / 128 / 256 and up to 8 query heads per KV head the need stays below 1.3 MB on
-// a 148-SM part.  The general kernel (other dtypes and head sizes) runs several CTAs per SM with up to
+// (batch item, query head, split).  The streaming kernel runs one CTA per SM over all KV heads, so with
+// bf16 / f16 inputs, head_dim 64 / 128 / 256 and up to 8 query heads per KV head the need is one row per
+// query head and SM (2.5 MB for 16 heads of 256 on a 148-SM part); when that does not fit, the
+// register-staged tensor-core kernel with at most half as many rows takes the call.  The general kernel (other dtypes and head sizes) runs several CTAs per SM with up to
 // four heads each, and its need depends on that occupancy; it can exceed the array.  Either way the
 // launcher compares the exact need of every launch of the call with this size before it launches
 // anything and refuses the call when one does not fit.

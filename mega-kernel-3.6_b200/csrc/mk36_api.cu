@@ -167,6 +167,10 @@ int mk36_set_option(const char* name, int value) {
         options().static_scratch_limit = value > 0 ? value : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "attn_stream") == 0) {
+        options().attn_stream = value ? 1 : 0;
+        return MK36_OK;
+    }
     if (std::strcmp(name, "dense_stream") == 0) {
         options().dense_stream = value ? 1 : 0;
         return MK36_OK;

@@ -80,6 +80,7 @@ struct Options {
     int ring_mma = 0;       // 1: the MoE ring kernel contracts with mma.sync whatever the token count
     int moe_stream = 1;     // 0: launches of one or two tokens use the ring kernel instead of the stream kernel
     int moe_stages = 0;     // > 0: ring depth of the MoE stream kernel (default: chosen from the shapes)
+    int attn_stream = 1;    // 0: attention calls skip the streaming kernel (shared-memory ring) and use the register-staged one
     int dense_stream = 1;   // 0: one-token dense FFN calls use the tensor-core kernel instead of the streaming kernel
     int moe_static = 0;     // 1: the MoE stream kernel deals its gate/up chunks statically (no work counter)
     int static_scratch_limit = 0;  // > 0: mk36_full_attention_decode_static treats its array as this many bytes (test hook)

@@ -447,12 +447,13 @@ def build_qwen36_decode_tgraph(
 # ---------------------------------------------------------------------------------------------
 # Launch geometry of the kernels in csrc/: threads per CTA, grid-wide barriers per launch.  The numbers
 # mirror the constants of the .cu files (kStThreads, kRingThreads, kDenseThreads, kMmaAttnThreads,
-# kLinThreads); tests/test_host_api.py reads those files and fails when the two drift apart.
+# kLinThreads, kDsThreads, kAsThreads); tests/test_host_api.py reads those files and fails when the two drift apart.
 KERNEL_GEOMETRY = {
     "moe_decode_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 2},
     "moe_decode_ring_kernel": {"block": 416, "grid_barriers": 2, "max_tokens": 8},
     "dense_ffn_mma_kernel": {"block": 512, "grid_barriers": 1, "max_tokens": 8},
-    "attention_decode_mma_kernel": {"block": 256, "grid_barriers": 1},
+    "attention_decode_stream_kernel": {"block": 288, "grid_barriers": 1},
+    "dense_ffn_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 1},
     "linear_attention_kernel": {"block": 256, "grid_barriers": 0},
 }
 _SMEM_OPTIN = 232448   # bytes of shared memory one CTA may use on sm_100
@@ -501,8 +502,8 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             row = hkv * hd * 2
             launches.append(KernelLaunch(
                 name=f"layer_{li}_attention", entry_point="mk36_full_attention_decode", task_ids=(task.id,),
-                kernel="attention_decode_mma_kernel", grid=sms, block=KERNEL_GEOMETRY["attention_decode_mma_kernel"]["block"],
-                grid_barriers=KERNEL_GEOMETRY["attention_decode_mma_kernel"]["grid_barriers"], layer=li,
+                kernel="attention_decode_stream_kernel", grid=sms, block=KERNEL_GEOMETRY["attention_decode_stream_kernel"]["block"],
+                grid_barriers=KERNEL_GEOMETRY["attention_decode_stream_kernel"]["grid_barriers"], layer=li,
                 phases=(KernelPhase("split_kv_online_softmax", 2 * batch * context_len, row, "runtime"),
                         KernelPhase("merge_partials", 0, 0, "static")),
                 hbm_bytes=batch * (2 * context_len * row + 2 * hq * hd * 2)))
@@ -544,11 +545,12 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
         elif task.kind == "dense_down":
             group = by_layer.pop(li, []) + [task]
             I = cfg.intermediate_size
+            dense_kernel = "dense_ffn_stream_kernel" if batch == 1 else "dense_ffn_mma_kernel"  # one token streams, more use the tensor cores
             launches.append(KernelLaunch(
                 name=f"layer_{li}_dense_ffn", entry_point="mk36_dense_ffn_decode", task_ids=tuple(t.id for t in group),
-                kernel="dense_ffn_mma_kernel", launches=_ceil_div(batch, KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["max_tokens"]),
-                grid=sms, block=KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["block"],
-                grid_barriers=KERNEL_GEOMETRY["dense_ffn_mma_kernel"]["grid_barriers"], layer=li,
+                kernel=dense_kernel, launches=_ceil_div(batch, KERNEL_GEOMETRY[dense_kernel]["max_tokens"]),
+                grid=sms, block=KERNEL_GEOMETRY[dense_kernel]["block"],
+                grid_barriers=KERNEL_GEOMETRY[dense_kernel]["grid_barriers"], layer=li,
                 phases=(KernelPhase("rmsnorm_to_smem", 0, 0, "static"),
                         KernelPhase("gate_up_swiglu", 2 * I, H * 2, "static"),
                         KernelPhase("down_and_residual", H, I * 2, "static")),

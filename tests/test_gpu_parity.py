@@ -151,6 +151,23 @@ def test_attention_general_kernel_matches_oracle(name, cuda_device):
     assert_output_parity(got["out"], run_oracle(case, spec)["out"], what=name + " (general kernel)")
 
 
+@pytest.mark.parametrize("name", ["attn_tiny_bf16_t128", "attn_27b_bf16_t1000", "attn_35b_bf16_t4096", "attn_35b_bf16_b2_t2500"])
+def test_attention_register_staged_kernel_matches_oracle(name, cuda_device):
+    """Shapes that normally take the streaming attention kernel (shared-memory ring), forced through the
+    tensor-core kernel that stages the cache in registers: same tolerances."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    cabi.check(lib.mk36_set_option(b"attn_stream", 0))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(b"attn_stream", 1))
+    assert_output_parity(got["out"], run_oracle(case, spec)["out"], what=name + " (register-staged kernel)")
+
+
 @pytest.mark.parametrize("seq", [1, 2, 3, 17])
 def test_attention_short_context_keeps_its_weights_normalised(seq, cuda_device):
     """A few cached tokens: nothing averages out, so the soft-max weights must add up to one exactly as

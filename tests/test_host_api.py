@@ -130,7 +130,8 @@ def test_kernel_geometry_table_matches_the_cuda_sources():
     assert geo["moe_decode_ring_kernel"]["max_tokens"] == ring["kRingMaxTokens"]
     assert mpk_graph._RING_STAGE == ring["kRingStageBytes"]
     assert geo["dense_ffn_mma_kernel"]["block"] == constants("dense_ffn_mma.cu")["kDenseThreads"]
-    assert geo["attention_decode_mma_kernel"]["block"] == constants("attention_decode_mma.cu")["kMmaAttnThreads"]
+    assert geo["attention_decode_stream_kernel"]["block"] == constants("attention_decode_stream.cu")["kAsThreads"]
+    assert geo["dense_ffn_stream_kernel"]["block"] == constants("dense_ffn_stream.cu")["kDsThreads"]
     assert geo["linear_attention_kernel"]["block"] == constants("linear_attention_decode.cu")["kLinThreads"]
     # the grid barriers: one barrier_arrive per barrier in the kernel's source
     assert (csrc / "moe_decode_stream.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_stream_kernel"]["grid_barriers"]
