@@ -87,8 +87,10 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
  * function; tests use the switch to cover both).  MoE calls of one or two tokens normally run the
  * stream kernel (no grid barrier before the routing, dealt gate/up chunks); "moe_stream" = 0 sends
  * them to the ring kernel instead, "ring_mma" = 1 additionally makes the ring kernel contract with
- * tensor-core instructions whatever the token count.  "moe_stages" (0 = default, else 2..6) sets the
- * stream kernel's ring depth and "moe_static" = 1 makes it (and the dense streaming kernel) deal
+ * tensor-core instructions whatever the token count.  MoE calls of three or more tokens normally run
+ * the batch kernel, eight tokens per launch (one grid barrier, the same weight stream); "moe_batch"
+ * = 0 sends them to the ring kernel.  "moe_stages" (0 = default, else 2..6) sets the stream and
+ * batch kernels' ring depth and "moe_static" = 1 makes them (and the dense streaming kernel) deal
  * chunks without the work counter; both exist for measurements.  One-token dense FFN calls normally
  * run the streaming kernel; "dense_stream" = 0 sends them to the tensor-core kernel that serves the
  * larger batches.  Attention calls with bf16 / f16 caches normally run the streaming kernel (cache

@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "moe_decode.cu",
     "moe_decode_ring.cu",
     "moe_decode_stream.cu",
+    "moe_decode_batch.cu",
     "dense_ffn_decode.cu",
     "dense_ffn_mma.cu",
     "dense_ffn_stream.cu",

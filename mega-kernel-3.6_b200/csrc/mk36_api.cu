@@ -159,6 +159,10 @@ int mk36_set_option(const char* name, int value) {
         options().moe_stream = value ? 1 : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "moe_batch") == 0) {
+        options().moe_batch = value ? 1 : 0;
+        return MK36_OK;
+    }
     if (std::strcmp(name, "moe_stages") == 0) {
         options().moe_stages = value > 0 ? value : 0;
         return MK36_OK;

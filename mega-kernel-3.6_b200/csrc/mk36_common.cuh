@@ -79,6 +79,7 @@ struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
     int ring_mma = 0;       // 1: the MoE ring kernel contracts with mma.sync whatever the token count
     int moe_stream = 1;     // 0: launches of one or two tokens use the ring kernel instead of the stream kernel
+    int moe_batch = 1;      // 0: launches of three or more tokens use the ring kernel instead of the batch kernel
     int moe_stages = 0;     // > 0: ring depth of the MoE stream kernel (default: chosen from the shapes)
     int attn_stream = 1;    // 0: attention calls skip the streaming kernel (shared-memory ring) and use the register-staged one
     int dense_stream = 1;   // 0: one-token dense FFN calls use the tensor-core kernel instead of the streaming kernel
@@ -114,8 +115,8 @@ constexpr int kCtaTraceMaxCtas = 192;
 // CTA.  A word is valid for the running kernel when its tag is Control::epoch + 1; the epoch grows by one
 // per finished kernel, so the words never need clearing.  The mailboxes sit at a fixed offset of the
 // workspace that no kernel uses as scratch and mk36_workspace_init zeroes, so a stale bit pattern can
-// never pass for a tag.  (MoE stream kernel: router logits.)
-constexpr int kTagSlots = 512;
+// never pass for a tag.  (MoE stream and batch kernels: router logits, [token][expert].)
+constexpr int kTagSlots = 2048;
 constexpr int kMailboxMaxCtas = 256;
 constexpr size_t kMailboxOffset = size_t(16) << 20;
 constexpr size_t kMailboxBytes = (size_t)kMailboxMaxCtas * kTagSlots * 8;

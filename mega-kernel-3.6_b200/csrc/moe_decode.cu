@@ -648,6 +648,8 @@ int moe_decode_ring_launch(const mk36_moe_args* a, const mk36_comm* comm, void* 
                            bool* handled);
 int moe_decode_stream_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                              bool* handled);
+int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                            bool* handled);
 
 // `comm` (may be null) makes the kernels end with the cross-GPU sum of the ranks' partial outputs.
 int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -659,6 +661,10 @@ int moe_decode_launch(const mk36_moe_args* a, const mk36_comm* comm, void* works
         bool handled = false;
         if (options().moe_stream && !options().ring_mma) {
             rc = moe_decode_stream_launch(a, comm, workspace, workspace_bytes, stream, &handled);
+            if (rc != MK36_OK || handled) return rc;
+        }
+        if (options().moe_batch && !options().ring_mma) {
+            rc = moe_decode_batch_launch(a, comm, workspace, workspace_bytes, stream, &handled);
             if (rc != MK36_OK || handled) return rc;
         }
         rc = moe_decode_ring_launch(a, comm, workspace, workspace_bytes, stream, &handled);
@@ -748,8 +754,8 @@ size_t mk36_moe_workspace_bytes(const mk36_moe_args* a) {
     MoePlan plan;
     if (!plan_moe(*a, 227 * 1024, &plan)) return 0;
     size_t need = kControlBytes + plan.scratch_bytes;
-    // launches of one or two tokens of a 2-byte dtype use the stream kernel when the workspace also holds its mailboxes
-    if (a->dtype != MK36_F32 && a->batch <= 2 && need < kTaggedEnd) need = kTaggedEnd;
+    // 2-byte dtypes use the stream kernel (one or two tokens) or the batch kernel when the workspace also holds their mailboxes
+    if (a->dtype != MK36_F32 && need < kTaggedEnd) need = kTaggedEnd;
     return need;
 }
 

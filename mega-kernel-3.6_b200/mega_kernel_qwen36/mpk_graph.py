@@ -450,6 +450,7 @@ def build_qwen36_decode_tgraph(
 # kLinThreads, kDsThreads, kAsThreads); tests/test_host_api.py reads those files and fails when the two drift apart.
 KERNEL_GEOMETRY = {
     "moe_decode_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 2},
+    "moe_decode_batch_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 8},
     "moe_decode_ring_kernel": {"block": 416, "grid_barriers": 2, "max_tokens": 8},
     "dense_ffn_mma_kernel": {"block": 512, "grid_barriers": 1, "max_tokens": 8},
     "attention_decode_stream_kernel": {"block": 288, "grid_barriers": 1},
@@ -458,6 +459,14 @@ KERNEL_GEOMETRY = {
 }
 _SMEM_OPTIN = 232448   # bytes of shared memory one CTA may use on sm_100
 _RING_STAGE = 32768
+
+
+def moe_batch_kernel_fits(hidden: int, experts: int, top_k: int, intermediate: int, shared_intermediate: int, sms: int = 148) -> bool:
+    """Shape conditions of the launcher in csrc/moe_decode_batch.cu for launches of eight tokens."""
+    hr_max = -(-hidden // sms)
+    return (hidden % 256 == 0 and sms <= hidden <= 8 * 384 and intermediate % 32 == 0 and shared_intermediate % 32 == 0
+            and 0 < intermediate <= 512 and shared_intermediate <= 512 and 0 < top_k <= 8 and experts <= 256
+            and hr_max <= 16 and hr_max * intermediate * 2 <= _RING_STAGE and (-(-experts // sms) + 1) * 8 <= 24)
 
 
 def moe_ring_tokens_per_launch(hidden: int, top_k: int, intermediate: int, shared_intermediate: int, sms: int = 148) -> int:
@@ -525,9 +534,13 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             E, K = cfg.num_experts, cfg.num_experts_per_tok
             I, Is = cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
             distinct = min(batch * K, E)
-            # one or two tokens: the stream kernel; more: the ring kernel, as many tokens per launch as fit
+            # one or two tokens: the stream kernel; more: the batch kernel, eight tokens per launch (the ring
+            # kernel, which takes as many tokens per launch as fit beside its activations, for shapes it refuses)
             if batch <= KERNEL_GEOMETRY["moe_decode_stream_kernel"]["max_tokens"]:
                 kname, n_launches = "moe_decode_stream_kernel", 1
+            elif moe_batch_kernel_fits(H, E, K, I, Is, sms):
+                kname = "moe_decode_batch_kernel"
+                n_launches = _ceil_div(batch, KERNEL_GEOMETRY[kname]["max_tokens"])
             else:
                 kname = "moe_decode_ring_kernel"
                 n_launches = _ceil_div(batch, moe_ring_tokens_per_launch(H, K, I, Is, sms))

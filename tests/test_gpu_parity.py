@@ -118,6 +118,61 @@ def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device)
     assert_output_parity(got["out"], ref["out"], what=f"{name} ({option})")
 
 
+@pytest.mark.parametrize("name", ["moe_small_bf16_b3", "moe_35b_bf16_b4_s0", "moe_35b_bf16_b8_s2"])
+@pytest.mark.parametrize("option", ["moe_batch=0", "moe_static=1", "moe_stages=3"])
+def test_moe_batch_kernel_variants_match_oracle(name, option, cuda_device):
+    """Calls of three or more tokens run the batch kernel (eight tokens per launch); the same calls
+    through the ring kernel, and the batch kernel with statically dealt chunks or a shallower
+    ring, must meet the same tolerances."""
+    from mega_kernel_qwen36 import cabi
+
+    case = CASES_BY_NAME[name]
+    spec = build_inputs(case)
+    lib = cabi.load()
+    key, value = option.split("=")
+    default = {"moe_batch": 1, "moe_static": 0, "moe_stages": 0}[key]
+    cabi.check(lib.mk36_set_option(key.encode(), int(value)))
+    try:
+        got = run_cuda(case, spec, cuda_device)
+    finally:
+        cabi.check(lib.mk36_set_option(key.encode(), default))
+    ref = run_oracle(case, spec)
+    assert_indices_exact(got["indices"], ref["indices"])
+    torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+    assert_output_parity(got["out"], ref["out"], what=f"{name} ({option})")
+
+
+@pytest.mark.parametrize("shape,batch,dtype,same", [
+    ("small", 5, torch.float16, False),
+    ("small", 8, torch.bfloat16, True),
+    ("35b", 3, torch.bfloat16, False),
+    ("35b", 7, torch.bfloat16, False),
+    ("35b", 8, torch.bfloat16, True),
+    ("35b", 9, torch.bfloat16, False),
+    ("35b", 19, torch.bfloat16, False),
+], ids=lambda v: str(v).replace("torch.", ""))
+def test_moe_batch_kernel_ragged_and_shared_experts(shape, batch, dtype, same, cuda_device):
+    """Token counts that do not fill a launch of eight (3, 5, 7), that need a second and third launch
+    with a remainder (9 = 8 + 1, 19 = 8 + 8 + 3), and eight identical tokens, which all choose the
+    same experts, so that every expert block meets all eight activation vectors."""
+    from golden_cases import Case
+    from mega_kernel_qwen36 import synthetic as syn
+
+    shp = syn.MOE_SMALL if shape == "small" else syn.MOE_35B_A3B
+    t = syn.moe_tensors(shp, batch, 11 + batch, dtype)
+    if same:
+        t["x"] = t["x"][:1].repeat(batch, 1).contiguous()
+    case = Case(f"moe_{shape}_b{batch}", "moe", lambda: None)
+    spec = {"tensors": t, "top_k": shp.top_k}
+    got = run_cuda(case, spec, cuda_device)
+    ref = run_oracle(case, spec)
+    assert_indices_exact(got["indices"], ref["indices"])
+    torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
+    assert_output_parity(got["out"], ref["out"], what=case.name)
+    if same:
+        assert torch.equal(got["out"], got["out"][:1].expand_as(got["out"])), "identical tokens must give identical rows"
+
+
 @pytest.mark.parametrize("name", ["dense_mid_f16_b1", "dense_27b_bf16_b1"])
 def test_dense_one_token_through_the_tensor_core_kernel(name, cuda_device):
     """One-token dense FFN calls run the streaming kernel; the tensor-core kernel that serves larger

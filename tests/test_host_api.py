@@ -97,11 +97,14 @@ def test_b200_worker_defaults_and_kernel_schedule():
     assert dense.hbm_bytes == syn.dense_algorithmic_bytes(syn.DENSE_27B, 8) == 534_947_840
     data = json.loads(plan.to_json())
     assert data["worker_config"]["total_sms"] == 148 and len(data["kernel_schedule"]) == len(plan.kernel_schedule)
-    # eight tokens: the ring kernel, split into launches of as many tokens as its shared memory holds
+    # eight tokens: the batch kernel in one launch; nineteen: three launches
     plan8 = mk.build_qwen36_decode_tgraph(cfg, batch_size=8, num_layers=1, worker_config=wc).linearize(wc, batch_size=8)
     moe8 = {k.name: k for k in plan8.kernel_schedule}["layer_0_moe"]
-    assert (moe8.kernel, moe8.block, moe8.grid_barriers) == ("moe_decode_ring_kernel", 416, 2)
-    assert moe8.launches == -(-8 // mpk_graph.moe_ring_tokens_per_launch(2048, 8, 512, 512))
+    assert (moe8.kernel, moe8.block, moe8.grid_barriers, moe8.launches) == ("moe_decode_batch_kernel", 416, 1, 1)
+    plan19 = mk.build_qwen36_decode_tgraph(cfg, batch_size=19, num_layers=1, worker_config=wc).linearize(wc, batch_size=19)
+    assert {k.name: k for k in plan19.kernel_schedule}["layer_0_moe"].launches == 3
+    # the ring kernel takes as many tokens per launch as its shared memory holds beside the activations
+    assert mpk_graph.moe_ring_tokens_per_launch(2048, 8, 512, 512) in (1, 2, 4, 8)
 
 
 def test_kernel_geometry_table_matches_the_cuda_sources():
@@ -122,7 +125,10 @@ def test_kernel_geometry_table_matches_the_cuda_sources():
         return found
 
     geo = mpk_graph.KERNEL_GEOMETRY
-    st = constants("moe_decode_stream.cu")
+    st = constants("mk36_moe_stream.cuh")
+    assert geo["moe_decode_batch_kernel"]["block"] == st["kStThreads"]
+    assert geo["moe_decode_batch_kernel"]["max_tokens"] == constants("moe_decode_batch.cu")["kBtMaxTokens"]
+    assert (csrc / "moe_decode_batch.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_batch_kernel"]["grid_barriers"]
     assert geo["moe_decode_stream_kernel"]["block"] == st["kStThreads"]
     assert geo["moe_decode_stream_kernel"]["max_tokens"] == st["kStMaxTokens"]
     ring = constants("moe_decode_ring.cu")
