@@ -185,4 +185,61 @@ __device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned l
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+// ---- top-k of up to 256 router logits held eight per lane (expert e = lane + 32 j in slot j) ----
+// Keys are order-preserving unsigned images of the fp32 logits (larger logit = larger key, 0 = no
+// logit).  Every lane first sorts its eight (key, slot) pairs - a 19-exchange network, all lanes at
+// once - so that a selection round is one warp-wide maximum over the lanes' heads and a shift on the
+// winning lane: the selection is a chain of dependent warp-wide operations, and its length, not the
+// arithmetic, is what a launch of one token waits for.  Order: descending logit, lowest expert
+// index on equal logits (mega_kernel_qwen36/reference.py:30-33 selects with torch.topk; the
+// oracle fixes the order on ties the same way).
+__device__ __forceinline__ void topk_exchange(unsigned& ka, int& ia, unsigned& kb, int& ib) {
+    const bool sw = (kb > ka) || (kb == ka && ib < ia);
+    const unsigned k0 = sw ? kb : ka, k1 = sw ? ka : kb;
+    const int i0 = sw ? ib : ia, i1 = sw ? ia : ib;
+    ka = k0; kb = k1; ia = i0; ib = i1;
+}
+
+__device__ __forceinline__ unsigned topk_key(unsigned logit_bits) {
+    return (logit_bits & 0x80000000u) ? ~logit_bits : (logit_bits | 0x80000000u);
+}
+
+__device__ __forceinline__ float topk_logit(unsigned key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Calls emit(round, expert, logit) on the lane that holds round r's winner, for r = 0 .. K - 1.
+template <typename Emit>
+__device__ __forceinline__ void topk_select(unsigned (&k)[kStTopkPerLane], int K, int lane, Emit&& emit) {
+    static_assert(kStTopkPerLane == 8, "the exchange network below sorts eight keys");
+    int i[8] = {0, 1, 2, 3, 4, 5, 6, 7};
+#define MK36_CE(a, b) topk_exchange(k[a], i[a], k[b], i[b])
+    MK36_CE(0, 1); MK36_CE(2, 3); MK36_CE(4, 5); MK36_CE(6, 7);
+    MK36_CE(0, 2); MK36_CE(1, 3); MK36_CE(4, 6); MK36_CE(5, 7);
+    MK36_CE(1, 2); MK36_CE(5, 6);
+    MK36_CE(0, 4); MK36_CE(1, 5); MK36_CE(2, 6); MK36_CE(3, 7);
+    MK36_CE(2, 4); MK36_CE(3, 5);
+    MK36_CE(1, 2); MK36_CE(3, 4); MK36_CE(5, 6);
+#undef MK36_CE
+#pragma unroll 1
+    for (int r = 0; r < K; ++r) {
+        const unsigned kmax = __reduce_max_sync(kFullMask, k[0]);
+        bool mine = (k[0] == kmax);
+        const unsigned tie = __ballot_sync(kFullMask, mine);
+        if (tie & (tie - 1u)) {  // several lanes hold the maximum: the lowest expert index wins
+            const unsigned cand = mine ? (unsigned)(lane + 32 * i[0]) : 0xffffffffu;
+            mine = (cand == __reduce_min_sync(kFullMask, cand));
+        }
+        if (mine) {
+            emit(r, lane + 32 * i[0], topk_logit(kmax));
+#pragma unroll
+            for (int j = 0; j + 1 < 8; ++j) {
+                k[j] = k[j + 1];
+                i[j] = i[j + 1];
+            }
+            k[7] = 0u;
+        }
+    }
+}
+
 }  // namespace mk36

@@ -34,6 +34,7 @@ namespace mk36 {
 
 constexpr int kBtMaxTokens = 8;
 constexpr int kBtMaxPublish = 24;  // (router row, token) logits one CTA publishes
+constexpr int kBtPairStride = 8;   // pair (token b, slot r) has index b * 8 + r whatever top_k is: the token of a pair is a shift away
 constexpr int kBtRowBatch = 7;     // down rows a warp keeps in flight: 14 rows per CTA split between two warps
 
 // Token b's routing, by one warp: waits for the token's logits in this CTA's mailbox (a word is valid
@@ -45,16 +46,16 @@ struct RouteArgs {
     Control* ctl;
     long long* indices;  // null unless this CTA reports the routing
     float* route_w;
-    unsigned long long* emask;  // shared memory, per expert: bit (b * K + slot) for every pair that chose it
+    unsigned long long* emask;  // shared memory, per expert, bit b * 8 + r: token b chose it in slot r (each byte has one writer)
     int E, K;
     int expert_base, local_experts;
 };
 __device__ __noinline__ bool route_token(const RouteArgs p, int b, unsigned tag, int* pair_e, float* pair_w, volatile int* abort_flag, int lane) {
     unsigned k8[kStTopkPerLane];
+    unsigned spins = 0;
     {
         const unsigned long long* box = p.box + (size_t)b * p.E;
-        const unsigned long long t0 = global_timer_ns();
-        unsigned spins = 0;
+        unsigned long long t0 = 0ull;  // the wait's clock starts at the first slow check: reading the timer is not free
         unsigned have = 0u;
         for (;;) {
             bool ready = true;
@@ -67,7 +68,7 @@ __device__ __noinline__ bool route_token(const RouteArgs p, int b, unsigned tag,
                         if ((unsigned)(w >> 32) == tag) {
                             have |= 1u << j;
                             const unsigned bits = (unsigned)w;
-                            k8[j] = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                            k8[j] = topk_key(bits);
                         } else {
                             ready = false;
                         }
@@ -80,8 +81,10 @@ __device__ __noinline__ bool route_token(const RouteArgs p, int b, unsigned tag,
             if ((++spins & 15u) == 0u) {
                 bool give_up = false;
                 if (lane == 0) {
+                    const unsigned long long now = global_timer_ns();
+                    if (t0 == 0ull) t0 = now;
                     if (*abort_flag != 0) give_up = true;
-                    else if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    else if (now - t0 > kWaitLimitNs) {
                         atomicCAS(&p.ctl->status, 0, kStatusMoeLogits);
                         *abort_flag = 1;
                         give_up = true;
@@ -91,44 +94,20 @@ __device__ __noinline__ bool route_token(const RouteArgs p, int b, unsigned tag,
             }
         }
     }
-    float first = 0.0f;
-#pragma unroll 1
-    for (int r = 0; r < p.K; ++r) {
-        unsigned m0 = k8[0], m1 = k8[2], m2 = k8[4], m3 = k8[6];
-        int j0 = 0, j1 = 2, j2 = 4, j3 = 6;
-        if (k8[1] > m0) { m0 = k8[1]; j0 = 1; }
-        if (k8[3] > m1) { m1 = k8[3]; j1 = 3; }
-        if (k8[5] > m2) { m2 = k8[5]; j2 = 5; }
-        if (k8[7] > m3) { m3 = k8[7]; j3 = 7; }
-        if (m1 > m0) { m0 = m1; j0 = j1; }
-        if (m3 > m2) { m2 = m3; j2 = j3; }
-        if (m2 > m0) { m0 = m2; j0 = j2; }
-        const unsigned kmax = __reduce_max_sync(kFullMask, m0);
-        bool mine = (m0 == kmax);
-        const unsigned tie = __ballot_sync(kFullMask, mine);
-        if (tie & (tie - 1u)) {  // several lanes hold the maximum: the lowest expert index wins
-            const unsigned cand = mine ? (unsigned)(lane + 32 * j0) : 0xffffffffu;
-            mine = (cand == __reduce_min_sync(kFullMask, cand));
-        }
-        const float best = __uint_as_float((kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax);
-        if (r == 0) first = best;
-        if (mine) {
-            const int e = lane + 32 * j0;
-            pair_e[b * p.K + r] = e;
-            pair_w[b * p.K + r] = best;
-            if (e >= p.expert_base && e < p.expert_base + p.local_experts) atomicOr(p.emask + e, 1ull << (b * p.K + r));
-#pragma unroll
-            for (int j = 0; j < kStTopkPerLane; ++j)
-                if (j == j0) k8[j] = 0u;
-        }
-    }
+    if (b == 0 && lane == 0) cta_stamp(p.ctl, blockIdx.x, 5);
+    topk_select(k8, p.K, lane, [&](int r, int e, float logit) {
+        pair_e[b * kBtPairStride + r] = e;
+        pair_w[b * kBtPairStride + r] = logit;
+        if (e >= p.expert_base && e < p.expert_base + p.local_experts) reinterpret_cast<unsigned char*>(p.emask)[e * 8 + b] = (unsigned char)(1u << r);
+    });
     __syncwarp();
-    const float ev = (lane < p.K) ? expf(pair_w[b * p.K + lane] - first) : 0.0f;
+    const float first = pair_w[b * kBtPairStride];
+    const float ev = (lane < p.K) ? expf(pair_w[b * kBtPairStride + lane] - first) : 0.0f;
     const float denom = warp_sum(ev);
     if (lane < p.K) {
         const float w = ev / denom;
-        pair_w[b * p.K + lane] = w;
-        if (p.indices) p.indices[(size_t)b * p.K + lane] = (long long)pair_e[b * p.K + lane];
+        pair_w[b * kBtPairStride + lane] = w;
+        if (p.indices) p.indices[(size_t)b * p.K + lane] = (long long)pair_e[b * kBtPairStride + lane];
         if (p.route_w) p.route_w[(size_t)b * p.K + lane] = w;
     }
     __syncwarp();
@@ -277,7 +256,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
     const int PR = p.pr;
     const size_t rowH = (size_t)p.H;
     const size_t up_off = (size_t)PR * rowH;
-    const int npairs = p.ntok * p.K;
+    const int npairs = p.ntok * kBtPairStride;
 
     const int r0 = fdiv(p.E * cta, p.fd_ncta), r1 = fdiv(p.E * (cta + 1), p.fd_ncta);
     const int s0 = fdiv(p.Is * cta, p.fd_ncta), s1 = fdiv(p.Is * (cta + 1), p.fd_ncta);
@@ -289,6 +268,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         trace_stamp(p.ctl, 0);
         p.ctl->trace[22] = (unsigned long long)clock64();
     }
+    if (tid == 0) cta_stamp(p.ctl, cta, 3);
 
     if (tid < 2 * kStMaxStages) mbar_init(&full_bar[tid], tid >= kStMaxStages ? kStConsumerWarps : 1);
     if (tid == 2 * kStMaxStages) mbar_init(topk_bar, (unsigned)p.ntok);
@@ -457,6 +437,14 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         dirty = ld_volatile_s32(&p.ctl->status);
         epoch = ld_volatile_u32(&p.ctl->epoch);
     }
+    // the mailboxes this CTA will write to and read from: one touch per 64 KB now, so that the address
+    // translations are resident when the logits are published (a first touch costs more than a microsecond)
+    {
+        const int nbox_touch = (ncta + p.box_share - 1) / p.box_share;
+        const size_t span = (size_t)nbox_touch * kTagSlots * 8;
+        const size_t at = (size_t)tid * 65536;
+        if (at < span) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const unsigned char*>(p.mailbox) + at));
+    }
     // the residual element this thread adds at the very end (one output element per thread): requested now
     float resid = 0.0f;
     {
@@ -601,6 +589,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         }
     }
     if (tracer) trace_stamp(p.ctl, 2);
+    if (tid == 0) cta_stamp(p.ctl, cta, 4);
 
     // ---- routing: warp b takes token b ----
     if (warp < p.ntok && *(volatile int*)&s_abort == 0) {
@@ -616,11 +605,13 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         ra.local_experts = p.local_experts;
         if (route_token(ra, warp, tag, s_pair_e, s_pair_w, (volatile int*)&s_abort, lane)) {
             if (lane == 0) mbar_arrive(topk_bar);
+            if (tid == 0) cta_stamp(p.ctl, cta, 6);
         }
     }
 
     bool ok = true;
-    int stage = 0, use = 0, owner = 0;
+    // chunk c is worked on by group (c + 2) % 3: the first chunk is the shared expert's, and groups 0 and 1 route
+    int stage = 0, use = 0, owner = kStGroups - 1;
     bool routed = false;
     int4 d = make_int4(kChunkEnd, 0, 0, 0);
     const int nchH = p.H >> 3;
@@ -668,14 +659,14 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
                         q1 = __ffsll((long long)m) - 1;
                         m &= m - 1;
                     }
-                    const int b0 = is_routed ? fdiv(q0, p.fd_K) : q0;
+                    const int b0 = is_routed ? (q0 >> 3) : q0;
                     const T* x0 = xs + (size_t)b0 * rowH;
                     float* o0 = obase + (size_t)q0 * olen + d.z + r;
                     if (q1 < 0) {
                         const float4 s4 = pair_dot<T, 1>(g, u, x0, x0, nchH, lane);
                         if (lane == 0) *o0 = silu(s4.x) * s4.y;
                     } else {
-                        const int b1 = is_routed ? fdiv(q1, p.fd_K) : q1;
+                        const int b1 = is_routed ? (q1 >> 3) : q1;
                         const float4 s4 = pair_dot<T, 2>(g, u, x0, xs + (size_t)b1 * rowH, nchH, lane);
                         if (lane == 0) {
                             *o0 = silu(s4.x) * s4.y;
@@ -695,6 +686,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
     // ---- the grid barrier: every CTA's activations are in the scratch buffers ----
     if (tracer) trace_stamp(p.ctl, 6);
     named_barrier(1, kStConsumerThreads);
+    if (tid == 0) cta_stamp(p.ctl, cta, 0);
     if (tid == 0) {
         bool fine = ok && (*(volatile int*)&s_abort == 0);
         if (fine) {
@@ -707,6 +699,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
     }
     named_barrier(1, kStConsumerThreads);
     if (tracer) trace_stamp(p.ctl, 7);
+    if (tid == 0) cta_stamp(p.ctl, cta, 1);
     if (!s_flag) return;  // every consumer warp leaves; the producer sees the abort flag in its waits
     const int n_unique = s_unique;
 
@@ -772,6 +765,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
     if (tracer) trace_stamp(p.ctl, 14);
     if (!ok) atomicCAS(&p.ctl->status, 0, kStatusMoeRingConsumer);
     named_barrier(1, kStConsumerThreads);
+    if (tid == 0) cta_stamp(p.ctl, cta, 2);
     if (*(volatile int*)&s_abort != 0 || !ok) return;
 
     // ---- combine in slot order, add the residual, round once: one output element per thread ----
@@ -784,7 +778,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
             float v = 0.0f;
 #pragma unroll 4
             for (int k = 0; k < p.K; ++k) {
-                const int pair = b * p.K + k;
+                const int pair = b * kBtPairStride + k;
                 const int e = s_pair_e[pair];
                 if (e >= p.expert_base && e < p.expert_base + p.local_experts) v = fmaf(s_pair_w[pair], part[pair * p.hr_max + j], v);
             }
@@ -820,8 +814,8 @@ int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void*
     if (a->batch < 3) return MK36_OK;
     const int H = a->hidden, E = a->experts, K = a->top_k, I = a->intermediate, Is = a->shared_intermediate;
     int tb = kBtMaxTokens;
-    if (K <= 0 || K > 32 || I <= 0 || Is < 0 || E <= 0 || E > 32 * kStTopkPerLane) return MK36_OK;
-    while (tb > 2 && (tb * K > kStMaxPairs || tb * E > kTagSlots)) --tb;
+    if (K <= 0 || K > kBtPairStride || I <= 0 || Is < 0 || E <= 0 || E > 32 * kStTopkPerLane) return MK36_OK;
+    while (tb > 2 && (tb * kBtPairStride > kStMaxPairs || tb * E > kTagSlots)) --tb;
     if (tb < 3) return MK36_OK;
     if (a->batch < tb) tb = a->batch;
     if (H % 256 != 0 || I % 32 != 0 || Is % 32 != 0) return MK36_OK;  // a warp's 32 router pieces lie in one row
@@ -859,7 +853,7 @@ int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void*
         off += bytes;
         return (int)at;
     };
-    const int pairs = tb * K;
+    const int pairs = tb * kBtPairStride;
     p.off_bars = take((2 * kStMaxStages + 3) * 8, 16);
     p.off_desc = take(kStMaxStages * 16, 16);
     p.off_uniq_e = take(kStMaxPairs * 4, 16);

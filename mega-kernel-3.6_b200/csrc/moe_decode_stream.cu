@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_stream_kernel(const 
                                 if ((unsigned)(w >> 32) == tag) {
                                     have |= bit;
                                     const unsigned bits = (unsigned)w;
-                                    key[b][j] = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                                    key[b][j] = topk_key(bits);
                                 } else {
                                     ready = false;
                                 }
@@ -212,37 +212,12 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_stream_kernel(const 
             unsigned k8[kStTopkPerLane];
 #pragma unroll
             for (int j = 0; j < kStTopkPerLane; ++j) k8[j] = (NT > 1 && b == 1) ? key[NT - 1][j] : key[0][j];
-            float first = 0.0f;
-#pragma unroll 1
-            for (int r = 0; r < p.K; ++r) {
-                // the lane's best key as a tree; on equal keys the lower slot (= lower expert index) stays
-                unsigned m0 = k8[0], m1 = k8[2], m2 = k8[4], m3 = k8[6];
-                int j0 = 0, j1 = 2, j2 = 4, j3 = 6;
-                if (k8[1] > m0) { m0 = k8[1]; j0 = 1; }
-                if (k8[3] > m1) { m1 = k8[3]; j1 = 3; }
-                if (k8[5] > m2) { m2 = k8[5]; j2 = 5; }
-                if (k8[7] > m3) { m3 = k8[7]; j3 = 7; }
-                if (m1 > m0) { m0 = m1; j0 = j1; }
-                if (m3 > m2) { m2 = m3; j2 = j3; }
-                if (m2 > m0) { m0 = m2; j0 = j2; }
-                const unsigned kmax = __reduce_max_sync(kFullMask, m0);
-                bool mine = (m0 == kmax);
-                const unsigned tie = __ballot_sync(kFullMask, mine);
-                if (tie & (tie - 1u)) {  // several lanes hold the maximum: the lowest expert index wins
-                    const unsigned cand = mine ? (unsigned)(lane + 32 * j0) : 0xffffffffu;
-                    mine = (cand == __reduce_min_sync(kFullMask, cand));
-                }
-                const float best = __uint_as_float((kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax);
-                if (r == 0) first = best;
-                if (mine) {
-                    s_pair_e[b * p.K + r] = lane + 32 * j0;
-                    s_pair_w[b * p.K + r] = best;
-#pragma unroll
-                    for (int j = 0; j < kStTopkPerLane; ++j)
-                        if (j == j0) k8[j] = 0u;
-                }
-            }
+            topk_select(k8, p.K, lane, [&](int r, int e, float logit) {
+                s_pair_e[b * p.K + r] = e;
+                s_pair_w[b * p.K + r] = logit;
+            });
             __syncwarp();
+            const float first = s_pair_w[b * p.K];
             const float ev = (lane < p.K) ? expf(s_pair_w[b * p.K + lane] - first) : 0.0f;
             const float denom = warp_sum(ev);
             if (lane < p.K) {

@@ -173,6 +173,36 @@ def test_moe_batch_kernel_ragged_and_shared_experts(shape, batch, dtype, same, c
         assert torch.equal(got["out"], got["out"][:1].expand_as(got["out"])), "identical tokens must give identical rows"
 
 
+@pytest.mark.parametrize("batch", [1, 2, 8])
+def test_moe_equal_logits_go_to_the_lowest_expert_index(batch, cuda_device):
+    """Router rows e and e + 128 are made identical, and so are rows 5 and 70, so that every logit has a
+    bit-equal twin: in the same lane of the selecting warp (e and e + 128) and in another lane (5 and 70).
+    Selection order: descending logit, lowest expert index among equals; the eight winners are then four
+    pairs of twins, each pair in index order."""
+    from golden_cases import Case
+    from oracle import decode_oracle as oracle
+    from mega_kernel_qwen36 import synthetic as syn
+
+    shp = syn.MOE_35B_A3B
+    t = syn.moe_tensors(shp, batch, 5, torch.bfloat16)
+    rw = t["router_weight"].clone()
+    rw[128:] = rw[:128]
+    rw[70] = rw[5]
+    rw[198] = rw[5]
+    t["router_weight"] = rw
+    spec = {"tensors": t, "top_k": shp.top_k}
+    got = run_cuda(Case("moe_ties", "moe", lambda: None), spec, cuda_device)
+    _, _, _, logits = oracle.moe_decode_f64(t["x"], *[t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=shp.top_k)
+    order = torch.sort(logits, dim=-1, descending=True, stable=True).indices[:, : shp.top_k]
+    # the margin between the eighth and the ninth *distinct* logit decides whether fp32 and fp64 can disagree
+    for b in range(batch):
+        distinct = torch.sort(torch.unique(logits[b]), descending=True).values
+        assert float((distinct[:5] - distinct[1:6]).min()) > 1e-5
+    assert torch.equal(got["indices"], order), (got["indices"], order)
+    ref = oracle.moe_decode_f64(t["x"], *[t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=shp.top_k, indices=order)[0]
+    assert_output_parity(got["out"], ref.to(got["out"].dtype), what="moe with tied logits")
+
+
 @pytest.mark.parametrize("name", ["dense_mid_f16_b1", "dense_27b_bf16_b1"])
 def test_dense_one_token_through_the_tensor_core_kernel(name, cuda_device):
     """One-token dense FFN calls run the streaming kernel; the tensor-core kernel that serves larger
