@@ -437,14 +437,6 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         dirty = ld_volatile_s32(&p.ctl->status);
         epoch = ld_volatile_u32(&p.ctl->epoch);
     }
-    // the mailboxes this CTA will write to and read from: one touch per 64 KB now, so that the address
-    // translations are resident when the logits are published (a first touch costs more than a microsecond)
-    {
-        const int nbox_touch = (ncta + p.box_share - 1) / p.box_share;
-        const size_t span = (size_t)nbox_touch * kTagSlots * 8;
-        const size_t at = (size_t)tid * 65536;
-        if (at < span) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const unsigned char*>(p.mailbox) + at));
-    }
     // the residual element this thread adds at the very end (one output element per thread): requested now
     float resid = 0.0f;
     {
