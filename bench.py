@@ -54,7 +54,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel: read from the ncu
 # summary under profiles/ (a line "traffic_bytes_per_launch: N"); None where no capture exists.
-NCU_SUMMARY = {1: "moe_decode_stream_kernel_35b_b1.md"}
+NCU_SUMMARY = {1: "moe_decode_stream_kernel_35b_b1.md", 8: "moe_decode_batch_kernel_35b_b8.md"}
 
 
 def ncu_traffic_bytes(batch: int):
