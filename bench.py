@@ -236,7 +236,7 @@ def library_dense_bar(x, dw, n, record):
 
 def bench_others(device, steps: int, warmup: int, peak, only=None):
     """Dense FFN, attention and linear attention at their measured shapes (rotating buffers).
-    `only` ("dense", "attention" or "linear") restricts the run to one op, e.g. for a profiler."""
+    `only` ("dense", "attention", "linear" or "projection") restricts the run to one op, e.g. for a profiler."""
     import mega_kernel_qwen36 as mk
     from mega_kernel_qwen36 import synthetic as syn
 
@@ -308,6 +308,28 @@ def bench_others(device, steps: int, warmup: int, peak, only=None):
         record(f"linear_attention_b{batch}_resident_{nsteps}steps_per_step", ms, n2 * nsteps, per_step_bytes)
         del states, ins
         torch.cuda.empty_cache()
+
+    # decode-time projections of the 35B-A3B attention layer and the LM head: weight copies rotate so that
+    # the working set exceeds the L2 (the LM head's 1 GB already does)
+    if want("projection"):
+        shapes = (("qkv_proj_35b", syn.QKV_35B, True, False, False), ("attn_out_proj_35b", syn.OUT_PROJ_35B, False, True, False),
+                  ("lm_head_35b_argmax", syn.LM_HEAD_35B, True, False, True))
+        for name, (kin, nout), norm, residual, argmax in shapes:
+            for batch in (1, 8):
+                t = syn.projection_tensors(kin, nout, batch, seed=3, norm=norm, residual=residual)
+                d = {k_: v_.to(device) for k_, v_ in t.items()}
+                wbytes = kin * nout * 2
+                copies = max(1, (3 * L2_BYTES) // wbytes + 1) if wbytes < 3 * L2_BYTES else 2
+                ws = [d["weight"]] + [d["weight"].clone() for _ in range(copies - 1)]
+                call = lambda i: mk.linear_decode(d["x"], ws[i % copies], norm_weight=d.get("norm_weight"), residual=d.get("residual"),
+                                                  return_argmax=argmax)
+                call(0)
+                n = max(copies, min(steps, 100 if wbytes < 3 * L2_BYTES else 12))
+                fns = [(lambda i=i: call(i)) for i in range(n)]
+                ms, _, _, _ = time_graph(fns, min(warmup, 3), replays=5)
+                record(f"{name}_b{batch}", ms, n, syn.projection_algorithmic_bytes(kin, nout, batch, norm=norm, residual=residual))
+                del ws, d, t
+                torch.cuda.empty_cache()
     return out
 
 
@@ -448,7 +470,7 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="full weight sets to rotate over")
     ap.add_argument("--no-others", action="store_true", help="skip the context measurements of the other ops")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--others-only", choices=["dense", "attention", "linear"], default=None,
+    ap.add_argument("--others-only", choices=["dense", "attention", "linear", "projection"], default=None,
                     help="run only that op's context measurement (for profiling one kernel on a small case)")
     ap.add_argument("--collective", choices=["fused", "nccl"], default="fused",
                     help="N > 1: sum the ranks' partials inside the kernel over peer memory, or with an NCCL all-reduce")

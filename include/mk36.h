@@ -339,6 +339,45 @@ typedef struct mk36_linear_attention_steps_args {
 MK36_API int mk36_linear_attention_decode_steps(const mk36_linear_attention_steps_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Decode-time projection of one to eight tokens:
+ *     out[b, :] = weight . xin[b, :] (+ residual[b, :]),   xin = RMSNorm(x; norm_weight, eps) or x,
+ * with an optional arg-max over each output row.
+ *
+ * No counterpart among the reference's kernels: these are the `linear` (q/k/v projection),
+ * `linear_residual` (attention output projection plus residual) and `lm_head` / arg-max tasks that
+ * the reference's decode task graph names (mega_kernel_qwen36/mpk_graph.py:352-398, 418-427,
+ * 496-514) and leaves to the caller, whose decode layer takes q, k and v as inputs
+ * (mega_kernel_qwen36/ops.py:701-748).  Arithmetic as everywhere else in the reference: RMSNorm in
+ * fp32 with the result rounded to the tensors' dtype (mega_kernel_qwen36/reference.py:10-13), fp32
+ * accumulation, one rounding after the residual was added.
+ *
+ * Layouts: x [batch, in_features]; weight [out_features, in_features] (torch.nn.functional.linear);
+ * norm_weight [in_features] or NULL; residual [batch, out_features] or NULL; out
+ * [batch, out_features]; argmax int64 [batch] or NULL: the index of the largest value of the stored
+ * (rounded) output row, the lowest index among equals.  bf16 / f16; batch <= 8; in_features a
+ * multiple of 8, at most 16384, and batch x in_features x 2 bytes at most 64 KB (a count of three or
+ * five to seven tokens is padded to the next multiple of four for that bound).  Other shapes return
+ * MK36_ERR_UNSUPPORTED.  The workspace is used for its control block only (status word, arg-max
+ * slots): mk36_linear_workspace_bytes() bytes, initialised like every workspace.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mk36_linear_args {
+    const void* x;
+    const void* norm_weight;
+    const void* weight;
+    const void* residual;
+    void* out;
+    int64_t* argmax;
+    int32_t dtype;
+    int32_t batch;
+    int32_t in_features;
+    int32_t out_features;
+    float eps;
+} mk36_linear_args;
+
+MK36_API size_t mk36_linear_workspace_bytes(const mk36_linear_args* args);
+MK36_API int mk36_linear_decode(const mk36_linear_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Multi-GPU (one process per GPU, all GPUs on one NVLink / NVSwitch box).
  *
  * The reference is single-GPU; these entry points have no counterpart there.  They run the same

@@ -42,6 +42,7 @@ CUDA_SOURCES = [
     "attention_decode_stream.cu",
     "attention_decode_static.cu",
     "linear_attention_decode.cu",
+    "linear_decode.cu",
 ]
 LIB_NAME = "libmk36.so"
 
@@ -153,6 +154,10 @@ def build_extension(force: bool = False) -> Path:
         ext,
         f"-L{PKG}",
         "-l:" + LIB_NAME,
+        # the C++ runtime as a shared library, named before the driver's own -lstdc++: a toolchain that only
+        # ships libstdc++.a would otherwise put a second, uninitialised copy of the iostream machinery into the
+        # extension, and formatting a number into an error message would crash instead of raising
+        "-l:libstdc++.so.6",
         f"-L{torch_lib}",
         "-lc10",
         "-lc10_cuda",

@@ -1,0 +1,372 @@
+// Decode-time projection: out[b, :] = W . (RMSNorm(x[b, :]) or x[b, :]) (+ residual[b, :]) for one to
+// eight tokens, bf16 / f16, with an optional arg-max over the output row (the language-model head).
+//
+// These are the `linear`, `linear_residual` and `lm_head` tasks of the decode task graph
+// (mega_kernel_qwen36/mpk_graph.py:352-398, 418-427, 496-514): the reference's planner names them but
+// the reference has no kernel for them (its decode layer takes q, k and v as inputs,
+// mega_kernel_qwen36/ops.py:701-748).  The arithmetic follows the formulas the reference uses
+// everywhere else: `rms_norm` (mega_kernel_qwen36/reference.py:10-13, result rounded to the input
+// dtype), fp32 accumulation, one rounding of the result after the residual was added.
+//
+// A weight-streaming kernel like the dense FFN's, but without any cross-CTA dependency: a CTA owns
+// every `gridDim.x`-th chunk of consecutive weight rows, the producer warp starts the bulk copies of
+// its chunks at kernel entry (the weights do not depend on x), and the consumers normalise x into
+// shared memory while the first chunks are in flight.  No grid barrier, so an ordinary launch.
+//
+//   chunk = as many whole rows as fit 32 KB (8 rows at an inner dimension of 2048); row r of chunk k
+//   is contracted by warp (k * rows + r) % 8 against all tokens (up to four per pass over the row);
+//   every consumer warp observes and releases every chunk (see moe_decode_stream.cu).
+//
+// Arg-max: every warp keeps the best (value, row) of the rows it produced per token, on the rounded
+// output value with the lower row index winning ties (what arg-max over the stored output would
+// give); CTA-wide and then grid-wide maxima go through 64-bit atomic maxima of {ordered value,
+// ~row}; the last CTA to leave turns the winners into indices and clears the slots.
+#include "mk36_ring.cuh"
+
+namespace mk36 {
+
+constexpr int kLinConsumerWarps = 8;
+constexpr int kLinConsumerThreads = kLinConsumerWarps * 32;
+constexpr int kLinThreads = kLinConsumerThreads + 32;
+constexpr int kLinStageBytes = 32768;
+constexpr int kLinMaxStages = 6;
+constexpr int kLinMaxTokens = 8;
+constexpr int kLinMaxPieces = 8;  // 16-byte pieces of one token per consumer thread: inner dimension <= 16384
+
+struct LinearParams {
+    const void* x;
+    const void* norm_w;    // null: x is used as it is
+    const void* w;         // [N, K]
+    const void* residual;  // null or [ntok, N]
+    void* out;             // [ntok, N]
+    long long* argmax;     // null or [ntok]
+    Control* ctl;
+    int ntok, K, N;
+    float eps;
+    int rows;     // weight rows per chunk
+    int nchunks;
+    int nstages;
+    int off_x, off_ring, off_bars;
+};
+
+template <typename T>
+__device__ __forceinline__ void lin_unpack(const uint4& v, float (&f)[8]) {
+    Chunk8<T> c;
+    c.raw = v;
+    unpack8(c, f);
+}
+
+// One weight row against NV token vectors, all in shared memory; lane l reads the 16-byte pieces
+// l, l + 32, ... of each (conflict-free).
+template <typename T, int NV>
+__device__ __forceinline__ void row_dot(const T* w, const T* x, size_t xstride, int nch, int lane, float (&s)[NV]) {
+#pragma unroll
+    for (int t = 0; t < NV; ++t) s[t] = 0.0f;
+#pragma unroll 2
+    for (int c = lane; c < nch; c += 32) {
+        float fw[8];
+        lin_unpack<T>(lds128(w + 8 * c), fw);
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            float fx[8];
+            lin_unpack<T>(lds128(x + (size_t)t * xstride + 8 * c), fx);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[t] = fmaf(fw[i], fx[i], s[t]);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int t = 0; t < NV; ++t) s[t] += __shfl_xor_sync(kFullMask, s[t], off);
+    }
+}
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
+    const unsigned bits = __float_as_uint(v);
+    const unsigned key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    return ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - (unsigned)row);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const LinearParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_abort;
+    __shared__ float s_red[kLinConsumerWarps];
+    __shared__ unsigned long long s_best[kLinMaxTokens];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int ncta = gridDim.x;
+    const int cta = blockIdx.x;
+    const bool is_producer = (warp == kLinConsumerWarps);
+
+    T* xs = reinterpret_cast<T*>(smem + p.off_x);
+    unsigned char* ring = smem + p.off_ring;
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + p.off_bars);
+    unsigned long long* empty_bar = full_bar + kLinMaxStages;
+    const int R = p.nstages;
+    const size_t rowK = (size_t)p.K;
+    const int my_chunks = (p.nchunks - cta + ncta - 1) / ncta;  // chunks cta, cta + ncta, ...
+
+    if (tid == 0 && cta == 0) trace_stamp(p.ctl, 0);
+    if (tid < 2 * kLinMaxStages) mbar_init(&full_bar[tid], tid >= kLinMaxStages ? kLinConsumerWarps : 1);
+    if (tid < kLinMaxTokens) s_best[tid] = 0ull;
+    if (tid == 0) s_abort = (ld_volatile_s32(&p.ctl->status) != 0) ? 1 : 0;  // nothing runs on a workspace whose status is set
+    if (tid < 32) mbar_init_fence();
+    __syncthreads();
+    if (s_abort) return;
+
+    // =====================================================================================
+    // Producer warp: this CTA's chunks, in order, as stages come free
+    // =====================================================================================
+    if (is_producer) {
+        if (lane != 0) return;
+        bool ok = true;
+        int stage = 0, use = 0;
+#pragma unroll 1
+        for (int k = 0; k < my_chunks && ok; ++k) {
+            const int c = cta + k * ncta;
+            const int first = c * p.rows;
+            const int count = min(p.rows, p.N - first);
+            if (use > 0) ok = mbar_wait(&empty_bar[stage], (unsigned)(use - 1) & 1u, &s_abort);
+            if (!ok) break;
+            const unsigned bytes = (unsigned)((size_t)count * rowK * sizeof(T));
+            mbar_arrive_expect_tx(&full_bar[stage], bytes);
+            bulk_copy_g2s(ring + (size_t)stage * kLinStageBytes, static_cast<const T*>(p.w) + (size_t)first * rowK, bytes, &full_bar[stage]);
+            if (++stage == R) { stage = 0; ++use; }
+        }
+        if (!ok) atomicCAS(&p.ctl->status, 0, kStatusLinearProducer);
+        // consumers wait on every barrier that was armed, so no copy is in flight when the CTA leaves
+        return;
+    }
+
+    // =====================================================================================
+    // Consumer warps
+    // =====================================================================================
+    // ---- x into shared memory as T, normalised when a norm weight is given (one token at a time:
+    //      thread t owns the 16-byte pieces t, t + 256, ...) ----
+    {
+        const int npieces = p.K >> 3;
+        const T* x = static_cast<const T*>(p.x);
+#pragma unroll 1
+        for (int b = 0; b < p.ntok; ++b) {
+            uint4 xv[kLinMaxPieces];
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kLinMaxPieces; ++i) {
+                const int piece = tid + i * kLinConsumerThreads;
+                xv[i] = make_uint4(0, 0, 0, 0);
+                if (piece < npieces) xv[i] = *reinterpret_cast<const uint4*>(x + (size_t)b * rowK + 8 * piece);
+            }
+            if (p.norm_w == nullptr) {
+#pragma unroll
+                for (int i = 0; i < kLinMaxPieces; ++i) {
+                    const int piece = tid + i * kLinConsumerThreads;
+                    if (piece < npieces) *reinterpret_cast<uint4*>(xs + (size_t)b * rowK + 8 * piece) = xv[i];
+                }
+                continue;
+            }
+#pragma unroll
+            for (int i = 0; i < kLinMaxPieces; ++i) {
+                float f[8];
+                lin_unpack<T>(xv[i], f);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) ss = fmaf(f[q], f[q], ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) s_red[warp] = ss;
+            named_barrier(1, kLinConsumerThreads);
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kLinConsumerWarps; ++w) tot += s_red[w];
+            const float rstd = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+#pragma unroll
+            for (int i = 0; i < kLinMaxPieces; ++i) {
+                const int piece = tid + i * kLinConsumerThreads;
+                if (piece < npieces) {
+                    float f[8], g[8];
+                    lin_unpack<T>(xv[i], f);
+                    lin_unpack<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + 8 * piece), g);
+                    T o[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) o[q] = from_float<T>(__fmul_rn(__fmul_rn(f[q], rstd), g[q]));
+                    *reinterpret_cast<uint4*>(xs + (size_t)b * rowK + 8 * piece) = *reinterpret_cast<const uint4*>(o);
+                }
+            }
+            named_barrier(1, kLinConsumerThreads);  // s_red is reused by the next token
+        }
+        named_barrier(1, kLinConsumerThreads);
+    }
+    if (tid == 0 && cta == 0) trace_stamp(p.ctl, 1);
+
+    // ---- the chunks ----
+    bool ok = true;
+    const int nch = p.K >> 3;
+    const T* resid = static_cast<const T*>(p.residual);
+    T* out = static_cast<T*>(p.out);
+    unsigned long long best0 = 0ull, best1 = 0ull;  // lane l < 4: the best of tokens l and 4 + l among this warp's rows
+    int stage = 0, use = 0, slot = 0;  // slot: (rows of the earlier chunks) % warps, the warp of the chunk's first row
+#pragma unroll 1
+    for (int k = 0; k < my_chunks; ++k) {
+        ok = mbar_wait(&full_bar[stage], (unsigned)use & 1u, &s_abort);
+        if (!ok) break;
+        const int first = (cta + k * ncta) * p.rows;
+        const int count = min(p.rows, p.N - first);
+        const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kLinStageBytes);
+        int r = warp - slot;
+        if (r < 0) r += kLinConsumerWarps;
+#pragma unroll 1
+        for (; r < count; r += kLinConsumerWarps) {
+            const T* wrow = sbase + (size_t)r * rowK;
+            const int n = first + r;
+#pragma unroll 1
+            for (int b0 = 0; b0 < p.ntok; b0 += 4) {
+                const int nb = min(4, p.ntok - b0);
+                const T* xb = xs + (size_t)b0 * rowK;
+                float s[4] = {0.f, 0.f, 0.f, 0.f};
+                if (nb == 1) {
+                    float s1[1];
+                    row_dot<T, 1>(wrow, xb, rowK, nch, lane, s1);
+                    s[0] = s1[0];
+                } else if (nb == 2) {
+                    float s2[2];
+                    row_dot<T, 2>(wrow, xb, rowK, nch, lane, s2);
+                    s[0] = s2[0];
+                    s[1] = s2[1];
+                } else {
+                    // three tokens run as four: the token area is padded to a multiple of four vectors
+                    row_dot<T, 4>(wrow, xb, rowK, nch, lane, s);
+                }
+                if (lane < nb) {
+                    float v = (lane == 0) ? s[0] : (lane == 1) ? s[1] : (lane == 2) ? s[2] : s[3];
+                    const size_t o = (size_t)(b0 + lane) * p.N + n;
+                    if (resid) v += to_float<T>(resid[o]);
+                    const T rounded = from_float<T>(v);
+                    out[o] = rounded;
+                    if (p.argmax) {
+                        const unsigned long long key = argmax_key(to_float<T>(rounded), n);
+                        if (b0 == 0) best0 = key > best0 ? key : best0;
+                        else best1 = key > best1 ? key : best1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (++stage == R) { stage = 0; ++use; }
+        slot += count;
+        while (slot >= kLinConsumerWarps) slot -= kLinConsumerWarps;
+    }
+    if (!ok) {
+        atomicCAS(&p.ctl->status, 0, kStatusLinearConsumer);
+        return;
+    }
+
+    // ---- arg-max: CTA-wide maxima first ----
+    if (p.argmax && lane < 4) {
+        if (best0 != 0ull) atomicMax(&s_best[lane], best0);
+        if (best1 != 0ull) atomicMax(&s_best[4 + lane], best1);
+    }
+    named_barrier(1, kLinConsumerThreads);
+    if (p.argmax && tid < p.ntok && s_best[tid] != 0ull) atomicMax(&p.ctl->best[tid], s_best[tid]);
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&p.ctl->ticket, 1u) == (unsigned)ncta - 1u) {
+            // the last CTA to leave: every CTA's maxima are in; publish and clear for the next kernel
+            __threadfence();
+            if (p.argmax) {
+                for (int b = 0; b < p.ntok; ++b) {
+                    const unsigned long long v = atomicExch(&p.ctl->best[b], 0ull);
+                    p.argmax[b] = (long long)(0xffffffffu - (unsigned)(v & 0xffffffffull));
+                }
+            }
+            p.ctl->ticket = 0u;
+            p.ctl->epoch = p.ctl->epoch + 1u;
+            __threadfence();
+            trace_stamp(p.ctl, 9);
+        }
+    }
+}
+
+}  // namespace mk36
+
+using namespace mk36;
+
+extern "C" {
+
+size_t mk36_linear_workspace_bytes(const mk36_linear_args* a) {
+    (void)a;
+    return kControlBytes;
+}
+
+int mk36_linear_decode(const mk36_linear_args* a, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!a) MK36_FAIL(MK36_ERR_INVALID_ARG, "linear_decode: args is NULL");
+    if (!a->x || !a->weight || !a->out) MK36_FAIL(MK36_ERR_INVALID_ARG, "linear_decode: NULL tensor pointer");
+    if (a->batch <= 0 || a->in_features <= 0 || a->out_features <= 0)
+        MK36_FAIL(MK36_ERR_INVALID_ARG, "linear_decode: sizes must be positive");
+    if (a->dtype != MK36_BF16 && a->dtype != MK36_F16)
+        MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: dtype must be bf16 or f16");
+    const int K = a->in_features, N = a->out_features;
+    if (a->batch > kLinMaxTokens) MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: at most %d tokens per call (got %d)", kLinMaxTokens, a->batch);
+    if (K % 8 != 0 || (size_t)K * 2 > (size_t)kLinStageBytes || K > 8 * kLinMaxPieces * kLinConsumerThreads)
+        MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: in_features must be a multiple of 8 and at most %d (got %d)", kLinStageBytes / 2, K);
+    if ((size_t)(a->batch > 2 ? (a->batch + 3) / 4 * 4 : a->batch) * K * 2 > 65536)
+        MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: batch x in_features x 2 bytes must fit 64 KB of shared memory");
+    if ((long long)N * K >= (1ll << 40) || N >= (1 << 30)) MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: out_features too large");
+    const void* ptrs[] = {a->x, a->weight, a->norm_weight, a->residual, a->out};
+    for (const void* q : ptrs)
+        if ((reinterpret_cast<uintptr_t>(q) & 15u) != 0) MK36_FAIL(MK36_ERR_INVALID_ARG, "linear_decode: tensors must be 16-byte aligned");
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        MK36_FAIL(MK36_ERR_WORKSPACE, "linear_decode: workspace is NULL or not 256-byte aligned");
+    if (workspace_bytes < kControlBytes)
+        MK36_FAIL(MK36_ERR_WORKSPACE, "linear_decode: workspace too small (%zu < %zu bytes)", workspace_bytes, (size_t)kControlBytes);
+    const DeviceInfo* dev = current_device_info();
+    if (!dev) return MK36_ERR_LAUNCH;
+
+    LinearParams p;
+    p.x = a->x;
+    p.norm_w = a->norm_weight;
+    p.w = a->weight;
+    p.residual = a->residual;
+    p.out = a->out;
+    p.argmax = reinterpret_cast<long long*>(a->argmax);
+    p.ctl = static_cast<Control*>(workspace);
+    p.ntok = a->batch;
+    p.K = K;
+    p.N = N;
+    p.eps = a->eps;
+    p.rows = kLinStageBytes / (K * 2);
+    p.nchunks = (N + p.rows - 1) / p.rows;
+    size_t off = 0;
+    auto take = [&](size_t bytes, size_t align) {
+        off = align_up(off, align);
+        const size_t at = off;
+        off += bytes;
+        return (int)at;
+    };
+    p.off_bars = take(2 * kLinMaxStages * 8, 16);
+    const int xtok = a->batch > 2 ? (a->batch + 3) / 4 * 4 : a->batch;  // groups of three tokens read a fourth vector
+    p.off_x = take((size_t)xtok * K * 2, 128);
+    p.off_ring = take(0, 128);
+    const long long room = (long long)dev->max_smem_optin - (long long)off - 1024;
+    int nstages = (int)(room / kLinStageBytes);
+    if (nstages > kLinMaxStages) nstages = kLinMaxStages;
+    if (nstages < 2) MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: shapes do not fit in shared memory");
+    p.nstages = nstages;
+    const size_t smem_bytes = (size_t)p.off_ring + (size_t)nstages * kLinStageBytes;
+    const int grid = p.nchunks < dev->sm_count ? p.nchunks : dev->sm_count;
+
+    const void* kernel = (a->dtype == MK36_BF16) ? (const void*)linear_decode_kernel<__nv_bfloat16> : (const void*)linear_decode_kernel<__half>;
+    {
+        const int rc = ensure_dynamic_smem(kernel, smem_bytes);
+        if (rc != MK36_OK) return rc;
+    }
+    void* params[] = {&p};
+    const cudaError_t e = cudaLaunchKernel(kernel, dim3(grid), dim3(kLinThreads), params, smem_bytes, stream);
+    if (e != cudaSuccess) MK36_FAIL(MK36_ERR_LAUNCH, "linear_decode: launch failed (grid %d, smem %zu): %s", grid, smem_bytes, cudaGetErrorString(e));
+    return MK36_OK;
+}
+
+}  // extern "C"

@@ -103,6 +103,8 @@ struct Control {
     // %globaltimer stamps (ns) written by CTA 0 of the last kernel that used this workspace, one
     // per phase boundary; read back with mk36_workspace_trace
     unsigned long long trace[kTraceSlots];
+    // grid-wide arg-max of the projection kernel: {ordered value, ~row} per token; zero between kernels
+    unsigned long long best[8];
 };
 // The control block is followed, inside the first kControlBytes, by per-CTA stamps: thread 0 of
 // CTA c writes slot s at kCtaTraceOffset + (c * kCtaTraceSlots + s) * 8 (read back with
@@ -130,6 +132,8 @@ constexpr int kStatusMoeBarrier1 = 101;
 constexpr int kStatusMoeBarrier2 = 102;
 constexpr int kStatusMoeRingProducer = 111;  // producer warp: a stage was never released
 constexpr int kStatusMoeRingConsumer = 112;  // consumer warp: a stage never filled
+constexpr int kStatusLinearProducer = 131;   // projection kernel: a stage was never released
+constexpr int kStatusLinearConsumer = 132;   // projection kernel: a stage never filled
 constexpr int kStatusMoeLogits = 121;        // stream kernel: another CTA's router logits never arrived
 constexpr int kStatusDenseBarrier = 201;
 constexpr int kStatusAttnBarrier = 301;

@@ -325,6 +325,48 @@ torch::Tensor dense_ffn_decode_partial(torch::Tensor x, torch::Tensor norm_weigh
 }
 
 // -------------------------------------------------------------------------------------------
+// linear_decode: out = weight . (RMSNorm(x) or x) (+ residual), optionally with the arg-max of each
+// output row.  Undefined tensors stand for "not given".  Returns (out, argmax or an empty tensor).
+// -------------------------------------------------------------------------------------------
+std::tuple<torch::Tensor, torch::Tensor> linear_decode(torch::Tensor x, torch::Tensor weight, c10::optional<torch::Tensor> norm_weight,
+                                                       c10::optional<torch::Tensor> residual, double eps, bool want_argmax) {
+    SHIM_CHECK_INPUT(x);
+    SHIM_CHECK_INPUT(weight);
+    TORCH_CHECK(x.dim() == 2, "x must be [batch, in_features]");
+    TORCH_CHECK(weight.dim() == 2 && weight.size(1) == x.size(1), "weight must be [out_features, in_features]");
+    TORCH_CHECK(weight.scalar_type() == x.scalar_type(), "x and weight dtype mismatch");
+    const c10::cuda::CUDAGuard guard(x.device());
+    mk36_linear_args a{};
+    a.x = x.data_ptr();
+    a.weight = weight.data_ptr();
+    if (norm_weight.has_value()) {
+        SHIM_CHECK_INPUT(norm_weight.value());
+        TORCH_CHECK(norm_weight->dim() == 1 && norm_weight->size(0) == x.size(1), "norm_weight must be [in_features]");
+        TORCH_CHECK(norm_weight->scalar_type() == x.scalar_type(), "x and norm_weight dtype mismatch");
+        a.norm_weight = norm_weight->data_ptr();
+    }
+    if (residual.has_value()) {
+        SHIM_CHECK_INPUT(residual.value());
+        TORCH_CHECK(residual->dim() == 2 && residual->size(0) == x.size(0) && residual->size(1) == weight.size(0),
+                    "residual must be [batch, out_features]");
+        TORCH_CHECK(residual->scalar_type() == x.scalar_type(), "x and residual dtype mismatch");
+        a.residual = residual->data_ptr();
+    }
+    a.dtype = dtype_code(x, "linear_decode");
+    a.batch = static_cast<int32_t>(x.size(0));
+    a.in_features = static_cast<int32_t>(x.size(1));
+    a.out_features = static_cast<int32_t>(weight.size(0));
+    a.eps = static_cast<float>(eps);
+    torch::Tensor out = torch::empty({x.size(0), weight.size(0)}, x.options());
+    a.out = out.data_ptr();
+    torch::Tensor best = torch::empty({want_argmax ? x.size(0) : 0}, x.options().dtype(torch::kInt64));
+    if (want_argmax) a.argmax = best.data_ptr<int64_t>();
+    Workspace& ws = workspace_for(x, mk36_linear_workspace_bytes(&a));
+    check_rc(mk36_linear_decode(&a, ws.buffer.data_ptr(), ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    return {out, best};
+}
+
+// -------------------------------------------------------------------------------------------
 // full_attention_decode: same name, arguments and return value as csrc/bindings.cpp:34.
 // -------------------------------------------------------------------------------------------
 torch::Tensor full_attention_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache, double scale) {
@@ -520,6 +562,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ipc_export", &ipc_export, "CUDA IPC handle of an exchange buffer");
     m.def("ipc_open", &ipc_open, "map a peer's exchange buffer; returns the device pointer in this process");
     m.def("ipc_close", &ipc_close);
+    m.def("linear_decode", &linear_decode, "decode-time projection with optional fused RMSNorm, residual and arg-max (sm_100a)");
     m.def("full_attention_decode", &full_attention_decode, "Qwen3.6 full-attention decode kernel (sm_100a)");
     m.def("linear_attention_decode", &linear_attention_decode, "Qwen3.6 linear-attention recurrent decode kernel (sm_100a)");
     m.def("linear_attention_decode_ex", &linear_attention_decode_ex, "per-head decay/beta, grouped keys, optional in-place state",

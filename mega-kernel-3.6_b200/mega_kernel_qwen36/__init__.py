@@ -33,6 +33,7 @@ from .ops import (
     apply_partial_rope,
     decode_layer,
     dense_ffn_decode,
+    linear_decode,
     extension_available,
     full_attention_decode,
     linear_attention_decode,
@@ -62,6 +63,7 @@ __all__ = [
     "build_qwen36_decode_tgraph",
     "decode_layer",
     "dense_ffn_decode",
+    "linear_decode",
     "extension_available",
     "full_attention_decode",
     "linear_attention_decode",

@@ -43,6 +43,15 @@ class DenseFfnArgs(C.Structure):
     ]
 
 
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("norm_weight", C.c_void_p), ("weight", C.c_void_p), ("residual", C.c_void_p),
+        ("out", C.c_void_p), ("argmax", C.c_void_p),
+        ("dtype", C.c_int32), ("batch", C.c_int32), ("in_features", C.c_int32), ("out_features", C.c_int32),
+        ("eps", C.c_float),
+    ]
+
+
 class AttentionArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("out", C.c_void_p),
@@ -94,6 +103,8 @@ SIGNATURES = {
     "mk36_moe_decode": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_dense_ffn_workspace_bytes": (C.c_size_t, [C.POINTER(DenseFfnArgs)]),
     "mk36_dense_ffn_decode": (C.c_int, [C.POINTER(DenseFfnArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mk36_linear_workspace_bytes": (C.c_size_t, [C.POINTER(LinearArgs)]),
+    "mk36_linear_decode": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_attention_workspace_bytes": (C.c_size_t, [C.POINTER(AttentionArgs)]),
     "mk36_full_attention_decode": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mk36_full_attention_decode_static": (C.c_int, [C.POINTER(AttentionArgs), C.c_void_p]),

@@ -159,6 +159,27 @@ def dense_ffn_decode(
     return ext.dense_ffn_decode(*tensors, float(eps), bool(add_residual))
 
 
+def linear_decode(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    *,
+    norm_weight: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    eps: float = 1e-6,
+    return_argmax: bool = False,
+):
+    """Decode-time projection ``weight @ (rms_norm(x) or x) (+ residual)`` for up to eight tokens.
+
+    The `linear` (q/k/v), `linear_residual` (attention output) and `lm_head` tasks of the decode task
+    graph (mpk_graph.py), which the reference plans but leaves to the caller.  x [B, K]; weight [N, K];
+    norm_weight [K] fuses the RMSNorm (rounded to x.dtype, as reference.py:10-13 does); residual
+    [B, N] is added in fp32 before the single rounding.  With ``return_argmax`` also returns int64 [B]:
+    arg-max of each stored output row, lowest index among equals."""
+    ext = _native("linear_decode", x, weight)
+    out, best = ext.linear_decode(x, weight, norm_weight, residual, float(eps), bool(return_argmax))
+    return (out, best) if return_argmax else out
+
+
 def apply_partial_rope(
     q: torch.Tensor,
     k: torch.Tensor,

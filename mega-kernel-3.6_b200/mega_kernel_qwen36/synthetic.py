@@ -225,3 +225,35 @@ def linear_algorithmic_bytes(batch: int, key_heads: int, value_heads: int, key_d
     state = 2 * batch * value_heads * key_dim * value_dim * 4
     vecs = batch * (2 * key_heads * key_dim + 2 * value_heads * value_dim) * elem
     return state + vecs
+
+
+# --------------------------------------------------------------------------------------------
+# Decode-time projections (the q/k/v projection, the attention output projection, the LM head)
+# --------------------------------------------------------------------------------------------
+# Qwen3.6-35B-A3B full-attention layer: hidden 2048; 16 query heads, 2 KV heads, head_dim 256.
+QKV_35B = (2048, 16 * 256 + 2 * 2 * 256)   # (in_features, out_features): hidden -> q | k | v
+OUT_PROJ_35B = (16 * 256, 2048)             # attention output -> hidden, plus residual
+LM_HEAD_35B = (2048, 248_320)               # hidden -> vocabulary
+
+
+def projection_tensors(in_features: int, out_features: int, batch: int, seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                       *, x_std: float = 1.0, w_std: float = 0.02, norm: bool = True, residual: bool = True,
+                       norm_jitter: float = 0.05) -> Dict[str, torch.Tensor]:
+    """x [batch, in]; weight [out, in]; optionally norm_weight [in] ~ N(1, jitter) and residual [batch, out]."""
+    rng = _rng(seed)
+    out = {"x": hidden_states(batch, in_features, seed, dtype, x_std=x_std),
+           "weight": _normal(rng, (out_features, in_features), w_std).to(dtype)}
+    if norm:
+        out["norm_weight"] = _normal(rng, (in_features,), norm_jitter, 1.0).to(dtype)
+    if residual:
+        out["residual"] = _normal(rng, (batch, out_features), x_std).to(dtype)
+    return out
+
+
+def projection_algorithmic_bytes(in_features: int, out_features: int, batch: int, *, norm: bool, residual: bool, elem: int = 2) -> int:
+    n = out_features * in_features * elem + batch * in_features * elem + batch * out_features * elem
+    if norm:
+        n += in_features * elem
+    if residual:
+        n += batch * out_features * elem
+    return n

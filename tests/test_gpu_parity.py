@@ -611,3 +611,74 @@ def test_c_abi_direct_call_matches_extension(cuda_device):
     assert b"sizes must be positive" in lib.mk36_last_error()
     args.hidden = 256
     assert lib.mk36_dense_ffn_decode(args, None, 0, stream) == cabi.MK36_ERR_WORKSPACE
+
+
+LINEAR_CASES = [
+    # batch, in_features, out_features, dtype, norm, residual
+    (1, 2048, 5120, torch.bfloat16, True, False),    # q | k | v projection of the 35B-A3B attention layer
+    (1, 4096, 2048, torch.bfloat16, False, True),    # attention output projection + residual
+    (1, 5120, 1024, torch.bfloat16, True, True),     # 27B hidden size: three rows per 32 KB chunk
+    (2, 2048, 1000, torch.float16, True, True),      # out_features not a multiple of the rows per chunk
+    (3, 256, 77, torch.bfloat16, True, False),       # three tokens run as a group of four; few chunks
+    (5, 1024, 4099, torch.float16, False, False),
+    (8, 2048, 5120, torch.bfloat16, True, True),
+    (8, 4096, 2048, torch.bfloat16, False, True),
+]
+
+
+@pytest.mark.parametrize("batch,k,n,dtype,norm,residual", LINEAR_CASES, ids=lambda v: str(v).replace("torch.", ""))
+def test_linear_decode_matches_oracle(batch, k, n, dtype, norm, residual, cuda_device):
+    """Decode-time projection (fused RMSNorm, residual) against the CPU oracle and its fp64 evaluation."""
+    import mega_kernel_qwen36 as mk
+    from oracle import decode_oracle as oracle
+    from mega_kernel_qwen36 import synthetic as syn
+
+    t = syn.projection_tensors(k, n, batch, seed=31 + batch, dtype=dtype, norm=norm, residual=residual)
+    d = {name: v.to(cuda_device) for name, v in t.items()}
+    got = mk.linear_decode(d["x"], d["weight"], norm_weight=d.get("norm_weight"), residual=d.get("residual")).cpu()
+    ref = oracle.linear_decode(t["x"], t["weight"], norm_weight=t.get("norm_weight"), residual=t.get("residual"))
+    assert got.dtype == dtype and got.shape == (batch, n)
+    assert_output_parity(got, ref, what=f"linear_decode {batch}x{k}->{n}")
+    f64 = oracle.linear_decode_f64(t["x"], t["weight"], norm_weight=t.get("norm_weight"), residual=t.get("residual"))
+    assert rel_l2(got.double(), f64) <= 5e-3
+    # the same call twice gives the same bits (no atomics on the data path)
+    again = mk.linear_decode(d["x"], d["weight"], norm_weight=d.get("norm_weight"), residual=d.get("residual")).cpu()
+    assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("batch,n", [(1, 30_001), (4, 248_320), (7, 9_000)])
+def test_linear_decode_argmax_is_the_argmax_of_the_stored_row(batch, n, cuda_device):
+    """LM-head use: the arg-max comes from the same launch; lowest index among equal (rounded) values."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+
+    k = 2048 if n > 100_000 else 512
+    t = syn.projection_tensors(k, n, batch, seed=5, dtype=torch.bfloat16, norm=True, residual=False)
+    d = {name: v.to(cuda_device) for name, v in t.items()}
+    for _ in range(2):  # the arg-max slots of the workspace must be clean again after a call
+        out, best = mk.linear_decode(d["x"], d["weight"], norm_weight=d["norm_weight"], return_argmax=True)
+        assert best.dtype == torch.int64 and best.shape == (batch,)
+        # torch.argmax does not promise the first index among equals; max + first match does
+        row_max = out.float().max(dim=-1, keepdim=True).values
+        first = (out.float() == row_max).float().argmax(dim=-1)
+        assert torch.equal(best, first), (best, first)
+    # rows whose top values tie after rounding: duplicate the best row of the weight further up
+    w = d["weight"].clone()
+    top = int(best[0])
+    later = (top + 1234) % n
+    w[later] = w[top]
+    out, best2 = mk.linear_decode(d["x"], w, norm_weight=d["norm_weight"], return_argmax=True)
+    assert int(best2[0]) == min(top, later)
+
+
+def test_linear_decode_refuses_what_it_does_not_take(cuda_device):
+    import mega_kernel_qwen36 as mk
+
+    x = torch.zeros(9, 256, dtype=torch.bfloat16, device=cuda_device)
+    w = torch.zeros(64, 256, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(RuntimeError, match="at most 8 tokens"):
+        mk.linear_decode(x, w)
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        mk.linear_decode(x[:1, :250].contiguous(), w[:, :250].contiguous())
+    with pytest.raises(RuntimeError, match="bf16 or f16|dtype"):
+        mk.linear_decode(x[:1].float(), w.float())

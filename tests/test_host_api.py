@@ -296,3 +296,26 @@ def test_ctypes_structures_match_the_c_header(tmp_path):
         assert seen[(cname, "size")] == __import__("ctypes").sizeof(ctype), cname
         for field, _ in ctype._fields_:
             assert seen[(cname, field)] == getattr(ctype, field).offset, f"{cname}.{field}"
+
+
+def test_extension_errors_with_formatted_numbers_raise_instead_of_crashing():
+    """An error message that formats a number goes through the C++ stream machinery of the extension;
+    an extension linked against a private static copy of the C++ runtime crashed there.  Run in a child
+    process so that a crash is a failure of this test only."""
+    import subprocess
+    import sys
+
+    if not mk.extension_available():
+        pytest.skip("extension not built")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import torch\n"
+        "from mega_kernel_qwen36 import _C as ext\n"
+        "try:\n"
+        "    ext.ipc_open('abc')\n"
+        "except RuntimeError as e:\n"
+        "    assert '64 bytes' in str(e), str(e)\n"
+        "    print('raised')\n"
+    ) % str(Path(mk.__file__).resolve().parent.parent)
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0 and "raised" in proc.stdout, (proc.returncode, proc.stderr[-500:])
