@@ -14,7 +14,8 @@
 // shared memory while the first chunks are in flight.  No grid barrier, so an ordinary launch.
 //
 //   chunk = as many whole rows as fit 32 KB (8 rows at an inner dimension of 2048); row r of chunk k
-//   is contracted by warp (k * rows + r) % 8 against all tokens (up to four per pass over the row);
+//   is contracted by warp (k * rows + r) % 8 against one or two tokens; with more tokens a warp takes four
+//   rows and four tokens at a time (rows4_dot4);
 //   every consumer warp observes and releases every chunk (see moe_decode_stream.cu).
 //
 // Arg-max: every warp keeps the best (value, row) of the rows it produced per token, on the rounded
@@ -46,6 +47,7 @@ struct LinearParams {
     int rows;     // weight rows per chunk
     int nchunks;
     int nstages;
+    int lg_ppt;   // log2 of the 16-byte pieces of one token per consumer thread, rounded up to a power of two
     int off_x, off_ring, off_bars;
 };
 
@@ -60,8 +62,12 @@ __device__ __forceinline__ void lin_unpack(const uint4& v, float (&f)[8]) {
 // l, l + 32, ... of each (conflict-free).
 template <typename T, int NV>
 __device__ __forceinline__ void row_dot(const T* w, const T* x, size_t xstride, int nch, int lane, float (&s)[NV]) {
+    // eight independent accumulators per token: the dependent chain is one FMA per piece, not eight
+    float acc[NV][8];
 #pragma unroll
-    for (int t = 0; t < NV; ++t) s[t] = 0.0f;
+    for (int t = 0; t < NV; ++t)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[t][i] = 0.0f;
 #pragma unroll 2
     for (int c = lane; c < nch; c += 32) {
         float fw[8];
@@ -71,13 +77,54 @@ __device__ __forceinline__ void row_dot(const T* w, const T* x, size_t xstride, 
             float fx[8];
             lin_unpack<T>(lds128(x + (size_t)t * xstride + 8 * c), fx);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s[t] = fmaf(fw[i], fx[i], s[t]);
+            for (int i = 0; i < 8; ++i) acc[t][i] = fmaf(fw[i], fx[i], acc[t][i]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NV; ++t)
+        s[t] = ((acc[t][0] + acc[t][1]) + (acc[t][2] + acc[t][3])) + ((acc[t][4] + acc[t][5]) + (acc[t][6] + acc[t][7]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int t = 0; t < NV; ++t) s[t] += __shfl_xor_sync(kFullMask, s[t], off);
+    }
+}
+
+// Up to four consecutive weight rows against four token vectors: every 16-byte piece of a token is read once
+// for the four rows and every piece of a row once for the four tokens, which keeps the shared-memory traffic
+// at twice the weight bytes (one row against four tokens read five pieces per weight piece and was bound by
+// shared-memory bandwidth).  Rows beyond `nrows` repeat the last row; their sums are not used.
+template <typename T>
+__device__ __forceinline__ void rows4_dot4(const T* w, size_t wstride, int nrows, const T* x, size_t xstride, int nch, int lane,
+                                           float (&s)[4][4]) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) s[r][t] = 0.0f;
+    const T* wr[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wr[r] = w + (size_t)min(r, nrows - 1) * wstride;
+#pragma unroll 1
+    for (int c = lane; c < nch; c += 32) {
+        float fx[4][8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) lin_unpack<T>(lds128(x + (size_t)t * xstride + 8 * c), fx[t]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float fw[8];
+            lin_unpack<T>(lds128(wr[r] + 8 * c), fw);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[r][t] = fmaf(fw[i], fx[t][i], s[r][t]);
         }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
-        for (int t = 0; t < NV; ++t) s[t] += __shfl_xor_sync(kFullMask, s[t], off);
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int t = 0; t < 4; ++t) s[r][t] += __shfl_xor_sync(kFullMask, s[r][t], off);
     }
 }
 
@@ -91,7 +138,8 @@ template <typename T>
 __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const LinearParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
-    __shared__ float s_red[kLinConsumerWarps];
+    __shared__ int s_dirty;  // the workspace's status word was set at entry: nothing is computed or stored
+    __shared__ float s_red[2][kLinConsumerWarps][kLinMaxPieces];
     __shared__ unsigned long long s_best[kLinMaxTokens];
 
     const int tid = threadIdx.x;
@@ -112,10 +160,12 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
     if (tid == 0 && cta == 0) trace_stamp(p.ctl, 0);
     if (tid < 2 * kLinMaxStages) mbar_init(&full_bar[tid], tid >= kLinMaxStages ? kLinConsumerWarps : 1);
     if (tid < kLinMaxTokens) s_best[tid] = 0ull;
-    if (tid == 0) s_abort = (ld_volatile_s32(&p.ctl->status) != 0) ? 1 : 0;  // nothing runs on a workspace whose status is set
+    if (tid == 0) {
+        s_abort = 0;
+        s_dirty = 0;
+    }
     if (tid < 32) mbar_init_fence();
     __syncthreads();
-    if (s_abort) return;
 
     // =====================================================================================
     // Producer warp: this CTA's chunks, in order, as stages come free
@@ -144,60 +194,163 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
     // =====================================================================================
     // Consumer warps
     // =====================================================================================
-    // ---- x into shared memory as T, normalised when a norm weight is given (one token at a time:
-    //      thread t owns the 16-byte pieces t, t + 256, ...) ----
-    {
+    // the status word: requested now, looked at after x is in shared memory.  On a workspace whose status is set
+    // nothing is computed or stored; the copies the producer has started are still waited for.
+    int dirty = 0;
+    if (tid == 0) dirty = ld_volatile_s32(&p.ctl->status);
+
+    // ---- x into shared memory as T, normalised when a norm weight is given.  A thread owns eight register
+    //      slots: slot j holds piece (tid + (j % ppt) * 256) of token (first + j / ppt), ppt = pieces of one
+    //      token per thread rounded up to a power of two, so that as many tokens as fit are loaded, reduced and
+    //      normalised in one pass with one block-wide exchange (the loads of x and of the norm weight are all
+    //      issued before anything waits). ----
+    if (p.ntok == 1) {
+        // one token: pieces tid, tid + 256, ... of x and of the norm weight, one block-wide sum
         const int npieces = p.K >> 3;
         const T* x = static_cast<const T*>(p.x);
-#pragma unroll 1
-        for (int b = 0; b < p.ntok; ++b) {
-            uint4 xv[kLinMaxPieces];
+        uint4 xv[kLinMaxPieces], wv[kLinMaxPieces];
+#pragma unroll
+        for (int i = 0; i < kLinMaxPieces; ++i) {
+            const int piece = tid + i * kLinConsumerThreads;
+            xv[i] = make_uint4(0, 0, 0, 0);
+            wv[i] = make_uint4(0, 0, 0, 0);
+            if (i < (1 << p.lg_ppt) && piece < npieces) {
+                xv[i] = *reinterpret_cast<const uint4*>(x + 8 * piece);
+                if (p.norm_w) wv[i] = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + 8 * piece);
+            }
+        }
+        float rstd = 1.0f;
+        if (p.norm_w) {
             float ss = 0.0f;
 #pragma unroll
             for (int i = 0; i < kLinMaxPieces; ++i) {
-                const int piece = tid + i * kLinConsumerThreads;
-                xv[i] = make_uint4(0, 0, 0, 0);
-                if (piece < npieces) xv[i] = *reinterpret_cast<const uint4*>(x + (size_t)b * rowK + 8 * piece);
-            }
-            if (p.norm_w == nullptr) {
+                if (i < (1 << p.lg_ppt)) {
+                    float f[8];
+                    lin_unpack<T>(xv[i], f);
 #pragma unroll
-                for (int i = 0; i < kLinMaxPieces; ++i) {
-                    const int piece = tid + i * kLinConsumerThreads;
-                    if (piece < npieces) *reinterpret_cast<uint4*>(xs + (size_t)b * rowK + 8 * piece) = xv[i];
+                    for (int q = 0; q < 8; ++q) ss = fmaf(f[q], f[q], ss);
                 }
-                continue;
-            }
-#pragma unroll
-            for (int i = 0; i < kLinMaxPieces; ++i) {
-                float f[8];
-                lin_unpack<T>(xv[i], f);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) ss = fmaf(f[q], f[q], ss);
             }
             ss = warp_sum(ss);
-            if (lane == 0) s_red[warp] = ss;
+            if (lane == 0) s_red[0][warp][0] = ss;
             named_barrier(1, kLinConsumerThreads);
             float tot = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kLinConsumerWarps; ++w) tot += s_red[w];
-            const float rstd = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            for (int w = 0; w < kLinConsumerWarps; ++w) tot += s_red[0][w][0];
+            rstd = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+        }
 #pragma unroll
-            for (int i = 0; i < kLinMaxPieces; ++i) {
-                const int piece = tid + i * kLinConsumerThreads;
-                if (piece < npieces) {
+        for (int i = 0; i < kLinMaxPieces; ++i) {
+            const int piece = tid + i * kLinConsumerThreads;
+            if (i < (1 << p.lg_ppt) && piece < npieces) {
+                if (p.norm_w) {
                     float f[8], g[8];
                     lin_unpack<T>(xv[i], f);
-                    lin_unpack<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + 8 * piece), g);
+                    lin_unpack<T>(wv[i], g);
                     T o[8];
 #pragma unroll
                     for (int q = 0; q < 8; ++q) o[q] = from_float<T>(__fmul_rn(__fmul_rn(f[q], rstd), g[q]));
+                    *reinterpret_cast<uint4*>(xs + 8 * piece) = *reinterpret_cast<const uint4*>(o);
+                } else {
+                    *reinterpret_cast<uint4*>(xs + 8 * piece) = xv[i];
+                }
+            }
+        }
+        if (tid == 0 && dirty != 0) s_dirty = 1;
+        named_barrier(1, kLinConsumerThreads);
+    } else {
+        const int npieces = p.K >> 3;
+        const T* x = static_cast<const T*>(p.x);
+        const int lg = p.lg_ppt, ppt = 1 << lg;
+        const int per_pass = kLinMaxPieces >> lg;  // tokens per pass
+        int parity = 0;
+#pragma unroll 1
+        for (int first_tok = 0; first_tok < p.ntok; first_tok += per_pass, parity ^= 1) {
+            uint4 xv[kLinMaxPieces], wv[kLinMaxPieces];
+#pragma unroll
+            for (int j = 0; j < kLinMaxPieces; ++j) {
+                const int b = first_tok + (j >> lg);
+                const int piece = tid + (j & (ppt - 1)) * kLinConsumerThreads;
+                const bool live = b < p.ntok && piece < npieces;
+                xv[j] = make_uint4(0, 0, 0, 0);
+                wv[j] = make_uint4(0, 0, 0, 0);
+                if (live) {
+                    xv[j] = *reinterpret_cast<const uint4*>(x + (size_t)b * rowK + 8 * piece);
+                    if (p.norm_w) wv[j] = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.norm_w) + 8 * piece);
+                }
+            }
+            if (p.norm_w == nullptr) {
+#pragma unroll
+                for (int j = 0; j < kLinMaxPieces; ++j) {
+                    const int b = first_tok + (j >> lg);
+                    const int piece = tid + (j & (ppt - 1)) * kLinConsumerThreads;
+                    if (b < p.ntok && piece < npieces) *reinterpret_cast<uint4*>(xs + (size_t)b * rowK + 8 * piece) = xv[j];
+                }
+                continue;
+            }
+            float ssj[kLinMaxPieces];
+#pragma unroll
+            for (int j = 0; j < kLinMaxPieces; ++j) {
+                float f[8];
+                lin_unpack<T>(xv[j], f);
+                float a = 0.0f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) a = fmaf(f[q], f[q], a);
+                ssj[j] = a;
+            }
+            float sst[kLinMaxPieces];  // per token of the pass
+#pragma unroll
+            for (int tk = 0; tk < kLinMaxPieces; ++tk) {
+                float a = 0.0f;
+#pragma unroll
+                for (int j = 0; j < kLinMaxPieces; ++j) a += ((j >> lg) == tk) ? ssj[j] : 0.0f;
+                sst[tk] = a;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+                for (int tk = 0; tk < kLinMaxPieces; ++tk) sst[tk] += __shfl_xor_sync(kFullMask, sst[tk], off);
+            }
+            if (lane < kLinMaxPieces) {
+                float v = sst[0];
+#pragma unroll
+                for (int tk = 1; tk < kLinMaxPieces; ++tk)
+                    if (lane == tk) v = sst[tk];
+                s_red[parity][warp][lane] = v;
+            }
+            named_barrier(1, kLinConsumerThreads);
+            float rstd[kLinMaxPieces];
+#pragma unroll
+            for (int tk = 0; tk < kLinMaxPieces; ++tk) {
+                float tot = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kLinConsumerWarps; ++w) tot += s_red[parity][w][tk];
+                rstd[tk] = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            }
+#pragma unroll
+            for (int j = 0; j < kLinMaxPieces; ++j) {
+                const int b = first_tok + (j >> lg);
+                const int piece = tid + (j & (ppt - 1)) * kLinConsumerThreads;
+                if (b < p.ntok && piece < npieces) {
+                    float rs = rstd[0];
+#pragma unroll
+                    for (int tk = 1; tk < kLinMaxPieces; ++tk)
+                        if ((j >> lg) == tk) rs = rstd[tk];
+                    float f[8], g[8];
+                    lin_unpack<T>(xv[j], f);
+                    lin_unpack<T>(wv[j], g);
+                    T o[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) o[q] = from_float<T>(__fmul_rn(__fmul_rn(f[q], rs), g[q]));
                     *reinterpret_cast<uint4*>(xs + (size_t)b * rowK + 8 * piece) = *reinterpret_cast<const uint4*>(o);
                 }
             }
-            named_barrier(1, kLinConsumerThreads);  // s_red is reused by the next token
+            // the next pass writes the other half of s_red; the one after it comes after this pass's barrier
         }
+        if (tid == 0 && dirty != 0) s_dirty = 1;
         named_barrier(1, kLinConsumerThreads);
     }
+    const bool dead = (s_dirty != 0);
     if (tid == 0 && cta == 0) trace_stamp(p.ctl, 1);
 
     // ---- the chunks ----
@@ -205,50 +358,87 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
     const int nch = p.K >> 3;
     const T* resid = static_cast<const T*>(p.residual);
     T* out = static_cast<T*>(p.out);
-    unsigned long long best0 = 0ull, best1 = 0ull;  // lane l < 4: the best of tokens l and 4 + l among this warp's rows
+    unsigned long long best0 = 0ull, best1 = 0ull;  // lane l < 16: the best of tokens l % 4 and 4 + l % 4 among the rows this lane stored
     int stage = 0, use = 0, slot = 0;  // slot: (rows of the earlier chunks) % warps, the warp of the chunk's first row
 #pragma unroll 1
     for (int k = 0; k < my_chunks; ++k) {
         ok = mbar_wait(&full_bar[stage], (unsigned)use & 1u, &s_abort);
         if (!ok) break;
+        if (tid == 0 && cta == 0 && k == 1) trace_stamp(p.ctl, 2);
+        if (dead) {  // only drain the copies
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (++stage == R) { stage = 0; ++use; }
+            continue;
+        }
         const int first = (cta + k * ncta) * p.rows;
         const int count = min(p.rows, p.N - first);
         const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kLinStageBytes);
+        if (p.ntok > 2) {
+            // groups of four rows, four tokens per pass: group g of the chunk goes to warp (slot + g) % warps
+            const int groups = (count + 3) >> 2;
+            int g = warp - slot;
+            if (g < 0) g += kLinConsumerWarps;
+#pragma unroll 1
+            for (; g < groups; g += kLinConsumerWarps) {
+                const int nrows = min(4, count - 4 * g);
+                const T* wrow = sbase + (size_t)(4 * g) * rowK;
+#pragma unroll 1
+                for (int b0 = 0; b0 < p.ntok; b0 += 4) {
+                    const int nb = min(4, p.ntok - b0);
+                    float s[4][4];
+                    rows4_dot4<T>(wrow, rowK, nrows, xs + (size_t)b0 * rowK, rowK, nch, lane, s);
+                    const int rr = lane >> 2, tt = lane & 3;
+                    if (lane < 16 && rr < nrows && tt < nb) {
+                        float v = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < 4; ++r)
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (rr == r && tt == t) v = s[r][t];
+                        const int n = first + 4 * g + rr;
+                        const size_t o = (size_t)(b0 + tt) * p.N + n;
+                        if (resid) v += to_float<T>(resid[o]);
+                        const T rounded = from_float<T>(v);
+                        out[o] = rounded;
+                        if (p.argmax) {
+                            const unsigned long long key = argmax_key(to_float<T>(rounded), n);
+                            if (b0 == 0) best0 = key > best0 ? key : best0;
+                            else best1 = key > best1 ? key : best1;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (++stage == R) { stage = 0; ++use; }
+            slot += groups;
+            while (slot >= kLinConsumerWarps) slot -= kLinConsumerWarps;
+            continue;
+        }
         int r = warp - slot;
         if (r < 0) r += kLinConsumerWarps;
 #pragma unroll 1
         for (; r < count; r += kLinConsumerWarps) {
             const T* wrow = sbase + (size_t)r * rowK;
             const int n = first + r;
-#pragma unroll 1
-            for (int b0 = 0; b0 < p.ntok; b0 += 4) {
-                const int nb = min(4, p.ntok - b0);
-                const T* xb = xs + (size_t)b0 * rowK;
-                float s[4] = {0.f, 0.f, 0.f, 0.f};
-                if (nb == 1) {
-                    float s1[1];
-                    row_dot<T, 1>(wrow, xb, rowK, nch, lane, s1);
-                    s[0] = s1[0];
-                } else if (nb == 2) {
-                    float s2[2];
-                    row_dot<T, 2>(wrow, xb, rowK, nch, lane, s2);
-                    s[0] = s2[0];
-                    s[1] = s2[1];
-                } else {
-                    // three tokens run as four: the token area is padded to a multiple of four vectors
-                    row_dot<T, 4>(wrow, xb, rowK, nch, lane, s);
-                }
-                if (lane < nb) {
-                    float v = (lane == 0) ? s[0] : (lane == 1) ? s[1] : (lane == 2) ? s[2] : s[3];
-                    const size_t o = (size_t)(b0 + lane) * p.N + n;
-                    if (resid) v += to_float<T>(resid[o]);
-                    const T rounded = from_float<T>(v);
-                    out[o] = rounded;
-                    if (p.argmax) {
-                        const unsigned long long key = argmax_key(to_float<T>(rounded), n);
-                        if (b0 == 0) best0 = key > best0 ? key : best0;
-                        else best1 = key > best1 ? key : best1;
-                    }
+            float s[2] = {0.f, 0.f};
+            if (p.ntok == 1) {
+                float s1[1];
+                row_dot<T, 1>(wrow, xs, rowK, nch, lane, s1);
+                s[0] = s1[0];
+            } else {
+                row_dot<T, 2>(wrow, xs, rowK, nch, lane, s);
+            }
+            if (lane < p.ntok) {
+                float v = (lane == 0) ? s[0] : s[1];
+                const size_t o = (size_t)lane * p.N + n;
+                if (resid) v += to_float<T>(resid[o]);
+                const T rounded = from_float<T>(v);
+                out[o] = rounded;
+                if (p.argmax) {
+                    const unsigned long long key = argmax_key(to_float<T>(rounded), n);
+                    best0 = key > best0 ? key : best0;
                 }
             }
         }
@@ -262,27 +452,27 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
         atomicCAS(&p.ctl->status, 0, kStatusLinearConsumer);
         return;
     }
+    if (dead) return;
+    if (tid == 0 && cta == ncta - 1) trace_stamp(p.ctl, 3);
 
     // ---- arg-max: CTA-wide maxima first ----
-    if (p.argmax && lane < 4) {
-        if (best0 != 0ull) atomicMax(&s_best[lane], best0);
-        if (best1 != 0ull) atomicMax(&s_best[4 + lane], best1);
+    if (p.argmax && lane < 16) {
+        if (best0 != 0ull) atomicMax(&s_best[lane & 3], best0);
+        if (best1 != 0ull) atomicMax(&s_best[4 + (lane & 3)], best1);
     }
+    if (!p.argmax) return;  // nothing crosses CTAs: the output rows are stored, the CTA is done
     named_barrier(1, kLinConsumerThreads);
-    if (p.argmax && tid < p.ntok && s_best[tid] != 0ull) atomicMax(&p.ctl->best[tid], s_best[tid]);
+    if (tid < p.ntok && s_best[tid] != 0ull) atomicMax(&p.ctl->best[tid], s_best[tid]);
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(&p.ctl->ticket, 1u) == (unsigned)ncta - 1u) {
             // the last CTA to leave: every CTA's maxima are in; publish and clear for the next kernel
             __threadfence();
-            if (p.argmax) {
-                for (int b = 0; b < p.ntok; ++b) {
-                    const unsigned long long v = atomicExch(&p.ctl->best[b], 0ull);
-                    p.argmax[b] = (long long)(0xffffffffu - (unsigned)(v & 0xffffffffull));
-                }
+            for (int b = 0; b < p.ntok; ++b) {
+                const unsigned long long v = atomicExch(&p.ctl->best[b], 0ull);
+                p.argmax[b] = (long long)(0xffffffffu - (unsigned)(v & 0xffffffffull));
             }
             p.ctl->ticket = 0u;
-            p.ctl->epoch = p.ctl->epoch + 1u;
             __threadfence();
             trace_stamp(p.ctl, 9);
         }
@@ -339,6 +529,11 @@ int mk36_linear_decode(const mk36_linear_args* a, void* workspace, size_t worksp
     p.eps = a->eps;
     p.rows = kLinStageBytes / (K * 2);
     p.nchunks = (N + p.rows - 1) / p.rows;
+    {
+        const int ppt = (K / 8 + kLinConsumerThreads - 1) / kLinConsumerThreads;
+        p.lg_ppt = 0;
+        while ((1 << p.lg_ppt) < ppt) ++p.lg_ppt;
+    }
     size_t off = 0;
     auto take = [&](size_t bytes, size_t align) {
         off = align_up(off, align);

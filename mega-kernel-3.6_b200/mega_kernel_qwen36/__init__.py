@@ -25,12 +25,14 @@ from .mpk_graph import (
     build_qwen36_decode_tgraph,
 )
 from .ops import (
+    AttentionBlockInputs,
     DecodeLayerResult,
     DenseFfnWeights,
     FullAttentionInputs,
     LinearAttentionInputs,
     MoeWeights,
     apply_partial_rope,
+    attention_block_decode,
     decode_layer,
     dense_ffn_decode,
     linear_decode,
@@ -43,6 +45,8 @@ from .ops import (
 )
 
 __all__ = [
+    "AttentionBlockInputs",
+    "attention_block_decode",
     "CompiledPlan",
     "DecodeLayerResult",
     "DenseFfnWeights",

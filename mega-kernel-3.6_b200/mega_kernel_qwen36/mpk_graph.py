@@ -456,6 +456,7 @@ KERNEL_GEOMETRY = {
     "attention_decode_stream_kernel": {"block": 288, "grid_barriers": 1},
     "dense_ffn_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 1},
     "linear_attention_kernel": {"block": 256, "grid_barriers": 0},
+    "linear_decode_kernel": {"block": 288, "grid_barriers": 0, "max_tokens": 8},
 }
 _SMEM_OPTIN = 232448   # bytes of shared memory one CTA may use on sm_100
 _RING_STAGE = 32768
@@ -504,6 +505,20 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
         return KernelLaunch(name=task.id, entry_point=None, task_ids=(task.id,), grid=task.grid_dim[0],
                             block=task.block_dim[0], grid_barriers=0)
 
+    held_norms: Dict[str, TaskSpec] = {}
+    held_head: List[TaskSpec] = []
+
+    def projection_launch(name: str, group, n_in: int, n_out: int, norm: bool, residual: bool, argmax: bool) -> KernelLaunch:
+        geo = KERNEL_GEOMETRY["linear_decode_kernel"]
+        rows = max(1, _RING_STAGE // (n_in * 2))
+        chunks = _ceil_div(n_out, rows)
+        phases = ((KernelPhase("rmsnorm_to_smem", 0, 0, "static"),) if norm else ()) + (
+            KernelPhase("weight_rows" + ("_residual" if residual else "") + ("_argmax" if argmax else ""), n_out, n_in * 2, "static"),)
+        nbytes = n_out * n_in * 2 + batch * (n_in + n_out) * 2 + (n_in * 2 if norm else 0) + (batch * n_out * 2 if residual else 0)
+        return KernelLaunch(name=name, entry_point="mk36_linear_decode", task_ids=tuple(t.id for t in group), kernel="linear_decode_kernel",
+                            launches=_ceil_div(batch, geo["max_tokens"]), grid=min(sms, chunks), block=geo["block"], grid_barriers=0,
+                            phases=phases, hbm_bytes=nbytes)
+
     for task in graph.topological_tasks():
         li = task.attrs.get("layer")
         if task.kind == "paged_attention":
@@ -525,6 +540,27 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
                 block=KERNEL_GEOMETRY["linear_attention_kernel"]["block"], grid_barriers=0, layer=li,
                 phases=(KernelPhase("state_update_and_readout", batch * hv * dk, dv * 4 * 2, "static"),),
                 hbm_bytes=2 * batch * hv * dk * dv * 4 + batch * (2 * hk * dk + 2 * hv * dv) * 2))
+        elif task.kind == "rmsnorm" and (task.id.endswith("_attn_norm") or task.id == "final_norm"):
+            layer_no = int(task.id.split("_")[1]) if task.id.startswith("layer_") else None
+            if layer_no is not None and cfg.layer_types[layer_no] != "full_attention":
+                launches.append(other(task))  # the recurrence's input norm: not one of this library's launches
+            else:
+                held_norms[task.id] = task  # fused into the projection that consumes it, if one follows
+        elif task.kind == "linear" and task.attrs.get("projection") == "qkv":
+            # RMSNorm + q | k | v projection: one launch of the projection kernel
+            L = task.id[: -len("_qkv_proj")]
+            norm = held_norms.pop(f"{L}_attn_norm", None)
+            n_out = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+            launches.append(projection_launch(f"{L}_qkv_proj", ([norm] if norm else []) + [task], H, n_out, norm is not None, False, False))
+        elif task.kind == "linear_residual" and not task.attrs.get("ffn"):
+            launches.append(projection_launch(task.id, [task], cfg.num_attention_heads * cfg.head_dim, H, False, True, False))
+        elif task.kind == "linear" and task.id == "lm_head":
+            held_head.append(task)
+        elif task.kind == "argmax" and held_head:
+            norm = held_norms.pop("final_norm", None)
+            launches.append(projection_launch("lm_head_argmax", ([norm] if norm else []) + held_head + [task], H, cfg.vocab_size,
+                                              norm is not None, False, True))
+            held_head.clear()
         elif task.kind == "rmsnorm" and task.attrs.get("ffn"):
             by_layer.setdefault(li, []).append(task)  # fused into the FFN launch below
         elif task.kind in ("moe_router", "moe_grouped_experts", "dense_gate_up"):
@@ -570,6 +606,9 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
                 hbm_bytes=3 * I * H * 2 + H * 2 + 2 * batch * H * 2))
         else:
             launches.append(other(task))
+    # norms and heads that no projection launch picked up (linear-attention layers, graphs without sampling)
+    for task in list(held_norms.values()) + held_head:
+        launches.append(other(task))
     assert not by_layer, f"unscheduled FFN tasks: {by_layer}"
     del tasks
     return tuple(launches)

@@ -73,6 +73,33 @@ class LinearAttentionInputs:
 
 
 @dataclass(frozen=True)
+class AttentionBlockInputs:
+    """A full-attention block with its projections: what the decode task graph calls `rmsnorm`, `linear`
+    (q | k | v), `attention` and `linear_residual` (mpk_graph.py).  No counterpart in the reference's ops,
+    whose decode layer starts from q and the caches.
+
+    qkv_weight [(Hq + 2 Hkv) * D, hidden]: rows of the query heads, then the key heads, then the value
+    heads.  out_weight [hidden, Hq * D].  k_cache / v_cache [B, T_max, Hkv, D] hold the first `position`
+    tokens; the new token's key and value are written at `position` (in place) and attention runs over
+    `position + 1` tokens.  cos / sin [rotary_dim] are those of `position`; they rotate the new query and
+    the new key only (the cache keeps rotated keys)."""
+
+    input_norm_weight: torch.Tensor
+    qkv_weight: torch.Tensor
+    out_weight: torch.Tensor
+    k_cache: torch.Tensor
+    v_cache: torch.Tensor
+    position: int
+    query_heads: int
+    kv_heads: int
+    head_dim: int
+    cos: Optional[torch.Tensor] = None
+    sin: Optional[torch.Tensor] = None
+    rotary_dim: int = 64
+    scale: Optional[float] = None
+
+
+@dataclass(frozen=True)
 class DecodeLayerResult:
     hidden: torch.Tensor
     router_indices: Optional[torch.Tensor] = None
@@ -216,6 +243,33 @@ def full_attention_decode(inputs: FullAttentionInputs) -> torch.Tensor:
     return ext.full_attention_decode(q.contiguous(), k_cache.contiguous(), inputs.v_cache.contiguous(), float(scale))
 
 
+def attention_block_decode(hidden: torch.Tensor, block: AttentionBlockInputs, *, eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """hidden [B, H] -> (hidden + out_proj(attention(q, cache)), attention output [B, Hq, D]).
+
+    Three launches: the fused RMSNorm + q|k|v projection, the attention kernel over the cache including
+    the new token, and the output projection with the residual added before the single rounding."""
+    hq, hkv, d = block.query_heads, block.kv_heads, block.head_dim
+    b = hidden.shape[0]
+    if block.qkv_weight.shape[0] != (hq + 2 * hkv) * d:
+        raise ValueError("qkv_weight must have (query_heads + 2 * kv_heads) * head_dim rows")
+    if not 0 <= block.position < block.k_cache.shape[1]:
+        raise ValueError("position must lie inside the cache")
+    qkv = linear_decode(hidden, block.qkv_weight, norm_weight=block.input_norm_weight, eps=eps)
+    q = qkv[:, : hq * d].reshape(b, hq, d)
+    k_new = qkv[:, hq * d : (hq + hkv) * d].reshape(b, 1, hkv, d)
+    v_new = qkv[:, (hq + hkv) * d :].reshape(b, 1, hkv, d)
+    q, k_new = apply_partial_rope(q, k_new, block.cos, block.sin, block.rotary_dim)
+    t = block.position + 1
+    block.k_cache[:, block.position : t] = k_new
+    block.v_cache[:, block.position : t] = v_new
+    k_used, v_used = block.k_cache[:, :t], block.v_cache[:, :t]
+    if not k_used.is_contiguous():  # batch > 1 with a cache longer than the context: the kernel wants dense [B, T, Hkv, D]
+        k_used, v_used = k_used.contiguous(), v_used.contiguous()
+    attn = full_attention_decode(FullAttentionInputs(q=q.contiguous(), k_cache=k_used, v_cache=v_used, scale=block.scale))
+    out = linear_decode(attn.reshape(b, hq * d), block.out_weight, residual=hidden)
+    return out, attn
+
+
 def linear_attention_decode(inputs: LinearAttentionInputs) -> Tuple[torch.Tensor, torch.Tensor]:
     """``S' = decay*S + k (x) v``, ``out = q^T S'``.  Returns ``(out, new_state)``; the input
     state is not modified."""
@@ -285,13 +339,17 @@ def decode_layer(
     layer_type: Optional[str] = None,
     eps: float = 1e-6,
     top_k: int = 8,
+    attention_block: Optional[AttentionBlockInputs] = None,
 ) -> DecodeLayerResult:
     """Token mixer (full attention every fourth layer, the linear recurrence otherwise), residual
     add, then the dense or MoE feed-forward with its own residual.  The mixer output is reshaped to
-    the hidden shape, so ``heads * head_dim`` must equal the hidden size (ops.py:722-729)."""
+    the hidden shape, so ``heads * head_dim`` must equal the hidden size (ops.py:722-729) - unless
+    ``attention_block`` supplies the block's own projections (an extension: any head geometry)."""
     kind = layer_type or qwen36_layer_type(layer_idx)
     attention_output = linear_output = linear_state = None
-    if kind == "full_attention":
+    if kind == "full_attention" and attention_block is not None:
+        stream, attention_output = attention_block_decode(hidden, attention_block, eps=eps)
+    elif kind == "full_attention":
         if full_attention is None:
             raise ValueError("full_attention inputs are required for full_attention layers")
         attention_output = full_attention_decode(full_attention).reshape_as(hidden)

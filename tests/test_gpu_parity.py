@@ -566,22 +566,33 @@ def test_status_word_is_sticky_until_the_workspace_is_initialised_again(cuda_dev
     a_args = cabi.AttentionArgs(q=t["q"].data_ptr(), k_cache=t["k_cache"].data_ptr(), v_cache=t["v_cache"].data_ptr(), out=a_out.data_ptr(),
                                 dtype=cabi.MK36_BF16, batch=1, query_heads=16, kv_heads=2, head_dim=256, seq_len=1024, scale=1.0 / 16)
 
+    pj = {k: v.to(dev) for k, v in syn.projection_tensors(2048, 1536, 2, seed=9).items()}
+    p_out = torch.full((2, 1536), 5.0, dtype=torch.bfloat16, device=dev)
+    p_best = torch.full((2,), -7, dtype=torch.int64, device=dev)
+    p_args = cabi.LinearArgs(x=pj["x"].data_ptr(), norm_weight=pj["norm_weight"].data_ptr(), weight=pj["weight"].data_ptr(),
+                             residual=pj["residual"].data_ptr(), out=p_out.data_ptr(), argmax=p_best.data_ptr(), dtype=cabi.MK36_BF16,
+                             batch=2, in_features=2048, out_features=1536, eps=1e-6)
+
     cabi.check(lib.mk36_selftest_bounded_wait(ws.data_ptr(), nbytes, stream, 20))
     cabi.check(lib.mk36_dense_ffn_decode(d_args, ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_moe_decode(m_args, ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_full_attention_decode(a_args, ws.data_ptr(), nbytes, stream))
+    cabi.check(lib.mk36_linear_decode(p_args, ws.data_ptr(), nbytes, stream))
     rc = lib.mk36_workspace_status(ws.data_ptr(), stream, ctypes.byref(status))
     assert rc == cabi.MK36_ERR_BARRIER_TIMEOUT and status.value == 901, (rc, status.value)
-    for name, out in (("dense", d_out), ("moe", m_out), ("attention", a_out)):
+    for name, out in (("dense", d_out), ("moe", m_out), ("attention", a_out), ("projection", p_out)):
         assert bool((out == 5.0).all()), f"{name}: an op queued behind a timeout wrote its output"
+    assert bool((p_best == -7).all())
 
     cabi.check(lib.mk36_workspace_init(ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_dense_ffn_decode(d_args, ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_moe_decode(m_args, ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_full_attention_decode(a_args, ws.data_ptr(), nbytes, stream))
+    cabi.check(lib.mk36_linear_decode(p_args, ws.data_ptr(), nbytes, stream))
     cabi.check(lib.mk36_workspace_status(ws.data_ptr(), stream, ctypes.byref(status)))
     assert status.value == 0
-    for name, out in (("dense", d_out), ("moe", m_out), ("attention", a_out)):
+    assert bool((p_best >= 0).all()) and bool((p_best < 1536).all())
+    for name, out in (("dense", d_out), ("moe", m_out), ("attention", a_out), ("projection", p_out)):
         assert torch.isfinite(out.float()).all() and not bool((out == 5.0).all()), name
 
 
@@ -682,3 +693,44 @@ def test_linear_decode_refuses_what_it_does_not_take(cuda_device):
         mk.linear_decode(x[:1, :250].contiguous(), w[:, :250].contiguous())
     with pytest.raises(RuntimeError, match="bf16 or f16|dtype"):
         mk.linear_decode(x[:1].float(), w.float())
+
+
+@pytest.mark.parametrize("batch,rope", [(1, True), (2, False)])
+def test_attention_block_with_projections_in_decode_layer(batch, rope, cuda_device):
+    """Full-attention layer at the 35B-A3B head geometry (16 query heads, 2 KV heads, head_dim 256: heads x
+    dim != hidden): fused norm + q|k|v projection, rotary on the new query and key, cache append, attention,
+    output projection + residual, then the MoE - against the same composition of the CPU oracle."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    H, hq, hkv, d, tmax, pos = 2048, 16, 2, 256, 384, 300
+    dev = cuda_device
+    moe_t = syn.moe_tensors(syn.MOE_35B_A3B, batch, seed=41)
+    hidden = moe_t["x"]
+    qkv = syn.projection_tensors(H, (hq + 2 * hkv) * d, batch, seed=42, norm=True, residual=False)
+    outp = syn.projection_tensors(hq * d, H, batch, seed=43, norm=False, residual=False)
+    cache = syn.attention_tensors(batch, hq, hkv, d, tmax, seed=44)
+    cos = sin = None
+    if rope:
+        ang = torch.arange(32, dtype=torch.float32) * 0.37 + 0.1
+        cos, sin = torch.cat((ang.cos(), ang.cos())), torch.cat((ang.sin(), ang.sin()))
+    block = mk.AttentionBlockInputs(
+        input_norm_weight=qkv["norm_weight"].to(dev), qkv_weight=qkv["weight"].to(dev), out_weight=outp["weight"].to(dev),
+        k_cache=cache["k_cache"].to(dev), v_cache=cache["v_cache"].to(dev), position=pos, query_heads=hq, kv_heads=hkv, head_dim=d,
+        cos=cos, sin=sin, rotary_dim=64, scale=1.0 / 16)
+    moe_w = mk.MoeWeights(*[moe_t[f].to(dev) for f in syn.MOE_WEIGHT_FIELDS])
+    r = mk.decode_layer(3, hidden.to(dev), moe_w, top_k=8, attention_block=block)
+
+    mid, attn, k_ref, v_ref = oracle.attention_block_decode(
+        hidden, qkv["norm_weight"], qkv["weight"], outp["weight"], cache["k_cache"], cache["v_cache"], pos, hq, hkv, d,
+        cos=cos, sin=sin, rotary_dim=64, scale=1.0 / 16)
+    want, idx, _ = oracle.moe_decode(mid, *[moe_t[f] for f in syn.MOE_WEIGHT_FIELDS], top_k=8)
+    assert_output_parity(r.attention_output.cpu(), attn, what="attention output")
+    assert_output_parity(block.k_cache[:, pos].cpu(), k_ref[:, pos], what="appended key")
+    assert_output_parity(block.v_cache[:, pos].cpu(), v_ref[:, pos], what="appended value")
+    assert torch.equal(block.k_cache[:, :pos].cpu(), cache["k_cache"][:, :pos])
+    if torch.equal(r.router_indices.cpu(), idx):  # a routing near-tie can flip an expert after three rounded stages
+        assert_output_parity(r.hidden.cpu(), want, what="layer output")
+    else:
+        assert (r.router_indices.cpu() == idx).float().mean() >= 0.9

@@ -88,7 +88,7 @@ def test_b200_worker_defaults_and_kernel_schedule():
     attn = launches["layer_3_attention"]
     assert attn.entry_point == "mk36_full_attention_decode" and attn.hbm_bytes == 67_125_248
     assert launches["layer_0_linear_attention"].hbm_bytes == 4_218_880
-    assert launches["layer_3_qkv_proj"].entry_point is None
+    assert launches["layer_3_qkv_proj"].entry_point == "mk36_linear_decode"
     # every task is scheduled exactly once
     scheduled = [tid for k in plan.kernel_schedule for tid in k.task_ids]
     assert sorted(scheduled) == sorted(t.id for t in plan.graph.tasks)
@@ -97,6 +97,17 @@ def test_b200_worker_defaults_and_kernel_schedule():
     assert dense.hbm_bytes == syn.dense_algorithmic_bytes(syn.DENSE_27B, 8) == 534_947_840
     data = json.loads(plan.to_json())
     assert data["worker_config"]["total_sms"] == 148 and len(data["kernel_schedule"]) == len(plan.kernel_schedule)
+    # the projections around the attention kernel and the LM head: launches of the projection kernel with the norms fused
+    full = mk.build_qwen36_decode_tgraph(cfg, batch_size=1, num_layers=4, worker_config=wc).linearize(wc, batch_size=1)
+    by_name = {k.name: k for k in full.kernel_schedule}
+    qkv, outp, head = by_name["layer_3_qkv_proj"], by_name["layer_3_attn_out_proj_residual"], by_name["lm_head_argmax"]
+    assert qkv.entry_point == outp.entry_point == head.entry_point == "mk36_linear_decode"
+    assert qkv.task_ids == ("layer_3_attn_norm", "layer_3_qkv_proj") and head.task_ids == ("final_norm", "lm_head", "argmax_or_sampler")
+    assert qkv.hbm_bytes == syn.projection_algorithmic_bytes(*syn.QKV_35B, 1, norm=True, residual=False)
+    assert outp.hbm_bytes == syn.projection_algorithmic_bytes(*syn.OUT_PROJ_35B, 1, norm=False, residual=True)
+    assert head.hbm_bytes == syn.projection_algorithmic_bytes(*syn.LM_HEAD_35B, 1, norm=True, residual=False)
+    assert (head.kernel, head.block, head.grid_barriers, head.grid) == ("linear_decode_kernel", 288, 0, 148)
+    assert by_name["layer_0_attn_norm"].entry_point is None
     # eight tokens: the batch kernel in one launch; nineteen: three launches
     plan8 = mk.build_qwen36_decode_tgraph(cfg, batch_size=8, num_layers=1, worker_config=wc).linearize(wc, batch_size=8)
     moe8 = {k.name: k for k in plan8.kernel_schedule}["layer_0_moe"]
@@ -139,6 +150,11 @@ def test_kernel_geometry_table_matches_the_cuda_sources():
     assert geo["attention_decode_stream_kernel"]["block"] == constants("attention_decode_stream.cu")["kAsThreads"]
     assert geo["dense_ffn_stream_kernel"]["block"] == constants("dense_ffn_stream.cu")["kDsThreads"]
     assert geo["linear_attention_kernel"]["block"] == constants("linear_attention_decode.cu")["kLinThreads"]
+    lin = constants("linear_decode.cu")
+    assert geo["linear_decode_kernel"]["block"] == lin["kLinThreads"]
+    assert geo["linear_decode_kernel"]["max_tokens"] == lin["kLinMaxTokens"]
+    assert mpk_graph._RING_STAGE == lin["kLinStageBytes"]
+    assert "barrier_arrive(" not in (csrc / "linear_decode.cu").read_text()
     # the grid barriers: one barrier_arrive per barrier in the kernel's source
     assert (csrc / "moe_decode_stream.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_stream_kernel"]["grid_barriers"]
     assert (csrc / "moe_decode_ring.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_ring_kernel"]["grid_barriers"]
