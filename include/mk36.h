@@ -90,8 +90,9 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
  * tensor-core instructions whatever the token count.  MoE calls of three or more tokens normally run
  * the batch kernel, eight tokens per launch (one grid barrier, the same weight stream); "moe_batch"
  * = 0 sends them to the ring kernel.  "moe_stages" (0 = default, else 2..6) sets the stream and
- * batch kernels' ring depth and "moe_static" = 1 makes them (and the dense streaming kernel) deal
- * chunks without the work counter; both exist for measurements.  One-token dense FFN calls normally
+ * batch kernels' ring depth, "moe_static" = 1 makes them (and the dense streaming kernel) deal
+ * chunks without the work counter, and "moe_dyn_rounds" (0 = default) sets how many of the last
+ * rounds of gate/up chunks go through that counter; these exist for measurements.  One-token dense FFN calls normally
  * run the streaming kernel; "dense_stream" = 0 sends them to the tensor-core kernel that serves the
  * larger batches.  Attention calls with bf16 / f16 caches normally run the streaming kernel (cache
  * chunks of all KV heads through a shared-memory ring); "attn_stream" = 0 sends them to the

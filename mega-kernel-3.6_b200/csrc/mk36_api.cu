@@ -179,6 +179,10 @@ int mk36_set_option(const char* name, int value) {
         options().dense_stream = value ? 1 : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "moe_dyn_rounds") == 0) {
+        options().moe_dyn_rounds = value > 0 ? value : 0;
+        return MK36_OK;
+    }
     if (std::strcmp(name, "moe_static") == 0) {
         options().moe_static = value ? 1 : 0;
         return MK36_OK;

@@ -56,6 +56,7 @@ struct MoeStreamParams {
     int unit_bytes;   // hr_max * I * sizeof(T): one expert's block of this CTA's down rows
     int upc;          // down blocks per ring stage
     int deal_static;  // 1: chunk k of CTA c is chunk k * ncta + c, no work counter
+    int dyn_rounds;   // rounds at the end of the gate/up stream that are dealt through the work counter
     FastDiv fd_ncta, fd_cpe, fd_K, fd_qi, fd_qis, fd_npr;
     int box_share;    // batch kernel: CTAs that read the same mailbox
     int off_emask;    // batch kernel: per expert, the (token, slot) pairs that chose it

@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
         {
             const int nchunks = n_unique * (int)p.fd_cpe.d;
             int static_rounds = fdiv(nchunks, p.fd_ncta);
-            if (!p.deal_static) static_rounds = max(static_rounds - 2, 0);
+            if (!p.deal_static) static_rounds = max(static_rounds - p.dyn_rounds, 0);
             const int dyn_base = static_rounds * ncta;
             int k = 0;
             int t_next = (k < static_rounds || p.deal_static) ? cta : dyn_base + (int)atomicAdd(&p.ctl->work_ticket, 1u);
@@ -899,6 +899,7 @@ int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void*
     p.unit_bytes = (int)unit_bytes;
     p.upc = (int)(kStStageBytes / unit_bytes);
     p.deal_static = options().moe_static ? 1 : 0;
+    p.dyn_rounds = options().moe_dyn_rounds > 0 ? options().moe_dyn_rounds : 2;
     p.fd_ncta = make_fastdiv(ncta);
     p.fd_cpe = make_fastdiv(I / pr);
     p.fd_K = make_fastdiv(K);
