@@ -104,22 +104,40 @@ static __device__ __noinline__ bool comm_poll_slow(const unsigned long long* add
 }
 
 // Sum over the ranks, in rank order, of element `idx` for step `step`; waits (bounded) for
-// contributions that have not arrived yet.  Returns false when one never arrives.
+// contributions that have not arrived yet.  Returns false when one never arrives.  The words of four ranks
+// are requested before the first of them is looked at: eight dependent round trips to L2 would cost more
+// than the exchange itself.
 __device__ __forceinline__ bool comm_get_sum(const CommParams& c, Control* ctl, unsigned step, size_t idx, float* sum) {
     const int parity = (int)(step & 1u);
     unsigned char* own = comm_buf(c, c.rank);
     float v = 0.0f;
-    for (int q = 0; q < c.world; ++q) {
-        const unsigned long long* addr = comm_slot(own, parity, q) + idx;
-        unsigned long long w;
-        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(addr) : "memory");
-        if ((unsigned)(w >> 32) != step + 1u) {
-            // once any wait of this kernel has given up the others do not start theirs: the kernel ends within
-            // one wait limit, not one per element
-            if (ld_volatile_s32(&ctl->status) != 0) return false;
-            if (!comm_poll_slow(addr, step + 1u, ctl, &w)) return false;
+    // four ranks at a time: all of a batch's words in flight together without holding sixteen registers
+#pragma unroll
+    for (int q0 = 0; q0 < kCommMaxRanks; q0 += 4) {
+        if (q0 >= c.world) break;
+        unsigned long long w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            w[j] = 0ull;
+            if (q0 + j < c.world) {
+                const unsigned long long* addr = comm_slot(own, parity, q0 + j) + idx;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[j]) : "l"(addr) : "memory");
+            }
         }
-        v += __uint_as_float((unsigned)w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (q0 + j < c.world) {
+                if ((unsigned)(w[j] >> 32) != step + 1u) {
+                    // once any wait of this kernel has given up the others do not start theirs: the kernel ends
+                    // within one wait limit, not one per element
+                    if (ld_volatile_s32(&ctl->status) != 0) return false;
+                    unsigned long long late;  // not &w[j]: taking its address would move the array to local memory
+                    if (!comm_poll_slow(comm_slot(own, parity, q0 + j) + idx, step + 1u, ctl, &late)) return false;
+                    w[j] = late;
+                }
+                v += __uint_as_float((unsigned)w[j]);
+            }
+        }
     }
     *sum = v;
     return true;
