@@ -29,6 +29,9 @@ def main() -> int:
     from oracle import decode_oracle as oracle
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    # every rank draws the full weights and runs the CPU oracle on them: share the host cores instead of
+    # letting `world` processes start one thread per core each
+    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
