@@ -234,7 +234,7 @@ def library_dense_bar(x, dw, n, record):
     record("dense_ffn_27b_b1_library_linear_bar", ms, n, syn.dense_algorithmic_bytes(syn.DENSE_27B, 1))
 
 
-def bench_others(device, steps: int, warmup: int, peak, only=None):
+def bench_others(device, steps: int, warmup: int, peak, only=None, shape_filter=None):
     """Dense FFN, attention and linear attention at their measured shapes (rotating buffers).
     `only` ("dense", "attention", "linear" or "projection") restricts the run to one op, e.g. for a profiler."""
     import mega_kernel_qwen36 as mk
@@ -315,6 +315,8 @@ def bench_others(device, steps: int, warmup: int, peak, only=None):
         shapes = (("qkv_proj_35b", syn.QKV_35B, True, False, False), ("attn_out_proj_35b", syn.OUT_PROJ_35B, False, True, False),
                   ("lm_head_35b_argmax", syn.LM_HEAD_35B, True, False, True))
         for name, (kin, nout), norm, residual, argmax in shapes:
+            if shape_filter and shape_filter not in name:
+                continue
             for batch in (1, 8):
                 t = syn.projection_tensors(kin, nout, batch, seed=3, norm=norm, residual=residual)
                 d = {k_: v_.to(device) for k_, v_ in t.items()}
@@ -468,6 +470,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--sets", type=int, default=4, help="full weight sets to rotate over")
+    ap.add_argument("--shape", default=None, help="with --others-only projection: only the shapes whose name contains this (e.g. lm_head)")
     ap.add_argument("--no-others", action="store_true", help="skip the context measurements of the other ops")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--others-only", choices=["dense", "attention", "linear", "projection"], default=None,
@@ -502,7 +505,7 @@ def main():
     if ns.others_only:
         # one of the context ops alone (small enough to sit under a profiler); not a bench line
         print(json.dumps({"others_only": ns.others_only, "steps": ns.steps,
-                          "others": bench_others(device, ns.steps, ns.warmup, peak, only=ns.others_only)}), flush=True)
+                          "others": bench_others(device, ns.steps, ns.warmup, peak, only=ns.others_only, shape_filter=ns.shape)}), flush=True)
         return
 
     host_weights, sets = build_moe_sets(device, ns.sets)
