@@ -84,12 +84,13 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
 
 /* Process-wide switches.  "force_generic" = 1 makes every op use its general register-streaming
  * kernel even where a specialised shared-memory-ring variant exists (the variants compute the same
- * function; tests use the switch to cover both).  MoE calls of one or two tokens normally run the
- * stream kernel (no grid barrier before the routing, dealt gate/up chunks); "moe_stream" = 0 sends
- * them to the ring kernel instead, "ring_mma" = 1 additionally makes the ring kernel contract with
- * tensor-core instructions whatever the token count.  MoE calls of three or more tokens normally run
- * the batch kernel, eight tokens per launch (one grid barrier, the same weight stream); "moe_batch"
- * = 0 sends them to the ring kernel.  "moe_stages" (0 = default, else 2..6) sets the stream and
+ * function; tests use the switch to cover both).  MoE calls of one token normally run the stream
+ * kernel (no grid barrier before the routing, dealt gate/up chunks) and calls of more tokens the
+ * batch kernel, eight tokens per launch (one grid barrier, the same weight stream).  "moe_stream"
+ * is the largest token count the stream kernel takes (default 1; 2 also sends two-token calls to
+ * it, 0 none); "moe_batch" = 0 sends what the stream kernel does not take to the ring kernel
+ * instead of the batch kernel; "ring_mma" = 1 additionally makes the ring kernel contract with
+ * tensor-core instructions whatever the token count.  "moe_stages" (0 = default, else 2..6) sets the stream and
  * batch kernels' ring depth, "moe_static" = 1 makes them (and the dense streaming kernel) deal
  * chunks without the work counter, and "moe_dyn_rounds" (0 = default) sets how many of the last
  * rounds of gate/up chunks go through that counter; these exist for measurements.  One-token dense FFN calls normally

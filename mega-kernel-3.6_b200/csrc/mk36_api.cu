@@ -156,7 +156,7 @@ int mk36_set_option(const char* name, int value) {
         return MK36_OK;
     }
     if (std::strcmp(name, "moe_stream") == 0) {
-        options().moe_stream = value ? 1 : 0;
+        options().moe_stream = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MK36_OK;
     }
     if (std::strcmp(name, "moe_batch") == 0) {

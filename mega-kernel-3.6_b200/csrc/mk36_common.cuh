@@ -78,12 +78,12 @@ inline FastDiv make_fastdiv(unsigned d) {
 struct Options {
     int force_generic = 0;  // 1: always use the register-streaming kernels, never the ring variants
     int ring_mma = 0;       // 1: the MoE ring kernel contracts with mma.sync whatever the token count
-    int moe_stream = 1;     // 0: launches of one or two tokens use the ring kernel instead of the stream kernel
-    int moe_batch = 1;      // 0: launches of three or more tokens use the ring kernel instead of the batch kernel
+    int moe_stream = 1;     // most tokens a call may have to run the stream kernel (0: never, 2: also two-token calls)
+    int moe_batch = 1;      // 0: calls the stream kernel does not take use the ring kernel instead of the batch kernel
     int moe_stages = 0;     // > 0: ring depth of the MoE stream kernel (default: chosen from the shapes)
     int attn_stream = 1;    // 0: attention calls skip the streaming kernel (shared-memory ring) and use the register-staged one
     int dense_stream = 1;   // 0: one-token dense FFN calls use the tensor-core kernel instead of the streaming kernel
-    int moe_dyn_rounds = 0; // > 0: rounds of gate/up chunks at the end of the stream dealt through the work counter (default: 4 for one or two tokens, 2 for more)
+    int moe_dyn_rounds = 0; // > 0: rounds of gate/up chunks at the end of the stream dealt through the work counter (default: 4 in the stream kernel, 2 in the batch kernel)
     int moe_static = 0;     // 1: the MoE stream kernel deals its gate/up chunks statically (no work counter)
     int static_scratch_limit = 0;  // > 0: mk36_full_attention_decode_static treats its array as this many bytes (test hook)
 };

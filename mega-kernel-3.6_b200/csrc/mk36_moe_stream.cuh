@@ -1,5 +1,5 @@
-// Pieces shared by the MoE streaming kernels (moe_decode_stream.cu: one or two tokens;
-// moe_decode_batch.cu: three to eight tokens): ring geometry, kernel parameters, the row-pair and
+// Pieces shared by the MoE streaming kernels (moe_decode_stream.cu: one token, two on request;
+// moe_decode_batch.cu: two to eight tokens): ring geometry, kernel parameters, the row-pair and
 // down-row contractions and the relaxed 64-bit loads / stores of the tagged mailbox words.
 #pragma once
 #include <cfloat>

@@ -1,4 +1,4 @@
-// MoE decode for launches of three to eight tokens on sm_100a (2-byte dtypes, aligned shapes): one
+// MoE decode for launches of two to eight tokens on sm_100a (2-byte dtypes, aligned shapes): one
 // launch, one grid barrier, one weight stream.  Same results as the general kernel in moe_decode.cu
 // (reference semantics: mega_kernel_qwen36/reference.py:16-62; the reference's CUDA kernel,
 // csrc/persistent_moe_decode.cu:477-581, takes the tokens of a step through seven grid-synchronised
@@ -797,18 +797,17 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
 // Host side
 // -------------------------------------------------------------------------------------------
 
-// Launches the batch kernel, eight tokens per launch, when the call suits it (three or more tokens, 2-byte
+// Launches the batch kernel, eight tokens per launch, when the call suits it (any token count; the dispatcher sends it calls of two or more; 2-byte
 // dtype, aligned shapes) and sets *handled; otherwise leaves *handled false (no error).
 int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                             bool* handled) {
     *handled = false;
     if (a->dtype != MK36_BF16 && a->dtype != MK36_F16) return MK36_OK;
-    if (a->batch < 3) return MK36_OK;
+    if (a->batch < 1) return MK36_OK;
     const int H = a->hidden, E = a->experts, K = a->top_k, I = a->intermediate, Is = a->shared_intermediate;
     int tb = kBtMaxTokens;
     if (K <= 0 || K > kBtPairStride || I <= 0 || Is < 0 || E <= 0 || E > 32 * kStTopkPerLane) return MK36_OK;
-    while (tb > 2 && (tb * kBtPairStride > kStMaxPairs || tb * E > kTagSlots)) --tb;
-    if (tb < 3) return MK36_OK;
+    while (tb > 1 && (tb * kBtPairStride > kStMaxPairs || tb * E > kTagSlots)) --tb;
     if (a->batch < tb) tb = a->batch;
     if (H % 256 != 0 || I % 32 != 0 || Is % 32 != 0) return MK36_OK;  // a warp's 32 router pieces lie in one row
     if (I > 512 || Is > 512) return MK36_OK;  // the down phase keeps an activation vector in registers, 16 values per lane

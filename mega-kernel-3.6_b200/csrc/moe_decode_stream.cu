@@ -1,4 +1,4 @@
-// MoE decode for launches of one or two tokens on sm_100a (2-byte dtypes, aligned shapes): the
+// MoE decode for launches of one token (two if asked to) on sm_100a (2-byte dtypes, aligned shapes): the
 // latency-critical case, where the step moves ~400 KB per SM and its time is a chain of dependent
 // latencies rather than a bandwidth problem.  Same results as the general kernel in moe_decode.cu
 // (reference semantics: mega_kernel_qwen36/reference.py:16-62); replaces the seven grid-synchronised

@@ -449,7 +449,7 @@ def build_qwen36_decode_tgraph(
 # mirror the constants of the .cu files (kStThreads, kRingThreads, kDenseThreads, kMmaAttnThreads,
 # kLinThreads, kDsThreads, kAsThreads); tests/test_host_api.py reads those files and fails when the two drift apart.
 KERNEL_GEOMETRY = {
-    "moe_decode_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 2},
+    "moe_decode_stream_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 1},
     "moe_decode_batch_kernel": {"block": 416, "grid_barriers": 1, "max_tokens": 8},
     "moe_decode_ring_kernel": {"block": 416, "grid_barriers": 2, "max_tokens": 8},
     "dense_ffn_mma_kernel": {"block": 512, "grid_barriers": 1, "max_tokens": 8},
@@ -570,7 +570,7 @@ def _kernel_schedule(graph: TaskGraph, wc: WorkerConfig, batch: int, context_len
             E, K = cfg.num_experts, cfg.num_experts_per_tok
             I, Is = cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
             distinct = min(batch * K, E)
-            # one or two tokens: the stream kernel; more: the batch kernel, eight tokens per launch (the ring
+            # one token: the stream kernel; more: the batch kernel, eight tokens per launch (the ring
             # kernel, which takes as many tokens per launch as fit beside its activations, for shapes it refuses)
             if batch <= KERNEL_GEOMETRY["moe_decode_stream_kernel"]["max_tokens"]:
                 kname, n_launches = "moe_decode_stream_kernel", 1

@@ -94,24 +94,34 @@ def test_moe_ring_kernel_tensor_core_consumers_match_oracle(name, cuda_device):
     assert_output_parity(got["out"], ref["out"], what=name + " (tensor-core consumers)")
 
 
-@pytest.mark.parametrize("name", ["moe_small_f16_b2", "moe_35b_bf16_b1_s0", "moe_35b_bf16_b2_s0"])
-@pytest.mark.parametrize("option", ["moe_stream=0", "moe_static=1", "moe_stages=3"])
-def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device):
-    """Calls of one or two tokens run the stream kernel; the same calls through the ring kernel's
-    plain-FMA consumers, and the stream kernel with statically dealt chunks or a shallower ring,
-    must meet the same tolerances."""
+MOE_DEFAULT_OPTIONS = {"moe_stream": 1, "moe_batch": 1, "moe_static": 0, "moe_stages": 0, "moe_dyn_rounds": 0}
+
+
+def _run_with_options(case, spec, device, options):
     from mega_kernel_qwen36 import cabi
 
+    lib = cabi.load()
+    pairs = [o.split("=") for o in options.split(",")]
+    for key, value in pairs:
+        cabi.check(lib.mk36_set_option(key.encode(), int(value)))
+    try:
+        return run_cuda(case, spec, device)
+    finally:
+        for key, _ in pairs:
+            cabi.check(lib.mk36_set_option(key.encode(), MOE_DEFAULT_OPTIONS[key]))
+
+
+@pytest.mark.parametrize("name", ["moe_small_f16_b2", "moe_35b_bf16_b1_s0", "moe_35b_bf16_b2_s0"])
+@pytest.mark.parametrize("option", ["moe_stream=2", "moe_stream=0", "moe_stream=0,moe_batch=0", "moe_stream=2,moe_static=1",
+                                    "moe_stream=2,moe_stages=3", "moe_stream=2,moe_dyn_rounds=7"])
+def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device):
+    """One-token calls run the stream kernel and two-token calls the batch kernel; the same calls through the
+    stream kernel at two tokens, the batch kernel at one, the ring kernel's plain-FMA consumers, and the stream
+    kernel with statically dealt chunks, a shallower ring or all rounds dealt through the counter must meet
+    the same tolerances."""
     case = CASES_BY_NAME[name]
     spec = build_inputs(case)
-    lib = cabi.load()
-    key, value = option.split("=")
-    default = {"moe_stream": 1, "moe_static": 0, "moe_stages": 0}[key]
-    cabi.check(lib.mk36_set_option(key.encode(), int(value)))
-    try:
-        got = run_cuda(case, spec, cuda_device)
-    finally:
-        cabi.check(lib.mk36_set_option(key.encode(), default))
+    got = _run_with_options(case, spec, cuda_device, option)
     ref = run_oracle(case, spec)
     assert_indices_exact(got["indices"], ref["indices"])
     torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)
@@ -119,23 +129,14 @@ def test_moe_small_batch_kernel_variants_match_oracle(name, option, cuda_device)
 
 
 @pytest.mark.parametrize("name", ["moe_small_bf16_b3", "moe_35b_bf16_b4_s0", "moe_35b_bf16_b8_s2"])
-@pytest.mark.parametrize("option", ["moe_batch=0", "moe_static=1", "moe_stages=3"])
+@pytest.mark.parametrize("option", ["moe_batch=0", "moe_static=1", "moe_stages=3", "moe_dyn_rounds=6"])
 def test_moe_batch_kernel_variants_match_oracle(name, option, cuda_device):
-    """Calls of three or more tokens run the batch kernel (eight tokens per launch); the same calls
-    through the ring kernel, and the batch kernel with statically dealt chunks or a shallower
-    ring, must meet the same tolerances."""
-    from mega_kernel_qwen36 import cabi
-
+    """Calls of two or more tokens run the batch kernel (eight tokens per launch); the same calls
+    through the ring kernel, and the batch kernel with statically dealt chunks, a shallower ring or more
+    rounds dealt through the counter, must meet the same tolerances."""
     case = CASES_BY_NAME[name]
     spec = build_inputs(case)
-    lib = cabi.load()
-    key, value = option.split("=")
-    default = {"moe_batch": 1, "moe_static": 0, "moe_stages": 0}[key]
-    cabi.check(lib.mk36_set_option(key.encode(), int(value)))
-    try:
-        got = run_cuda(case, spec, cuda_device)
-    finally:
-        cabi.check(lib.mk36_set_option(key.encode(), default))
+    got = _run_with_options(case, spec, cuda_device, option)
     ref = run_oracle(case, spec)
     assert_indices_exact(got["indices"], ref["indices"])
     torch.testing.assert_close(got["weights"], ref["weights"], atol=1e-5, rtol=1e-4)

@@ -141,7 +141,8 @@ def test_kernel_geometry_table_matches_the_cuda_sources():
     assert geo["moe_decode_batch_kernel"]["max_tokens"] == constants("moe_decode_batch.cu")["kBtMaxTokens"]
     assert (csrc / "moe_decode_batch.cu").read_text().count("barrier_arrive(p.ctl") == geo["moe_decode_batch_kernel"]["grid_barriers"]
     assert geo["moe_decode_stream_kernel"]["block"] == st["kStThreads"]
-    assert geo["moe_decode_stream_kernel"]["max_tokens"] == st["kStMaxTokens"]
+    assert geo["moe_decode_stream_kernel"]["max_tokens"] == 1 <= st["kStMaxTokens"]  # dispatched at one token; able to take two
+    assert re.search(r"int moe_stream = 1;", (csrc / "mk36_common.cuh").read_text())
     ring = constants("moe_decode_ring.cu")
     assert geo["moe_decode_ring_kernel"]["block"] == ring["kRingThreads"]
     assert geo["moe_decode_ring_kernel"]["max_tokens"] == ring["kRingMaxTokens"]
