@@ -97,7 +97,8 @@ MK36_API int mk36_workspace_status(void* workspace, void* stream, int* device_st
  * run the streaming kernel; "dense_stream" = 0 sends them to the tensor-core kernel that serves the
  * larger batches.  Attention calls with bf16 / f16 caches normally run the streaming kernel (cache
  * chunks of all KV heads through a shared-memory ring); "attn_stream" = 0 sends them to the
- * tensor-core kernel that stages the cache in registers.  Unknown names return
+ * tensor-core kernel that stages the cache in registers.  "linear_mma" is the smallest token count
+ * for which a projection (mk36_linear_decode) runs on tensor-core tiles (default 3, 0 = never).  Unknown names return
  * MK36_ERR_INVALID_ARG. */
 MK36_API int mk36_set_option(const char* name, int value);
 

@@ -22,6 +22,7 @@
 // output value with the lower row index winning ties (what arg-max over the stored output would
 // give); CTA-wide and then grid-wide maxima go through 64-bit atomic maxima of {ordered value,
 // ~row}; the last CTA to leave turns the winners into indices and clears the slots.
+#include "mk36_mma.cuh"
 #include "mk36_ring.cuh"
 
 namespace mk36 {
@@ -32,6 +33,7 @@ constexpr int kLinThreads = kLinConsumerThreads + 32;
 constexpr int kLinStageBytes = 32768;
 constexpr int kLinMaxStages = 6;
 constexpr int kLinMaxTokens = 8;
+constexpr int kLinMmaRows = 16;   // weight rows of one tensor-core tile
 constexpr int kLinMaxPieces = 8;  // 16-byte pieces of one token per consumer thread: inner dimension <= 16384
 
 struct LinearParams {
@@ -47,6 +49,8 @@ struct LinearParams {
     int rows;     // weight rows per chunk
     int nchunks;
     int nstages;
+    int mma;      // 1: three to eight tokens on tensor-core instructions (tokens are the eight columns of the tile)
+    int off_red;  // tensor-core path: the warps' partial tiles, two buffers
     int lg_ppt;   // log2 of the 16-byte pieces of one token per consumer thread, rounded up to a power of two
     int off_x, off_ring, off_bars;
 };
@@ -256,6 +260,10 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
                 }
             }
         }
+        if (p.mma) {
+            for (int i = tid; i < (kLinMaxTokens - 1) * npieces; i += kLinConsumerThreads)
+                *reinterpret_cast<uint4*>(xs + rowK + 8 * (size_t)i) = make_uint4(0, 0, 0, 0);
+        }
         if (tid == 0 && dirty != 0) s_dirty = 1;
         named_barrier(1, kLinConsumerThreads);
     } else {
@@ -347,6 +355,12 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
             }
             // the next pass writes the other half of s_red; the one after it comes after this pass's barrier
         }
+        if (p.mma) {
+            // the tile has eight token columns: the ones beyond the batch are zero
+            const int npieces8 = (kLinMaxTokens - p.ntok) * (p.K >> 3);
+            for (int i = tid; i < npieces8; i += kLinConsumerThreads)
+                *reinterpret_cast<uint4*>(xs + (size_t)p.ntok * rowK + 8 * (size_t)i) = make_uint4(0, 0, 0, 0);
+        }
         if (tid == 0 && dirty != 0) s_dirty = 1;
         named_barrier(1, kLinConsumerThreads);
     }
@@ -374,6 +388,55 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
         const int first = (cta + k * ncta) * p.rows;
         const int count = min(p.rows, p.N - first);
         const T* sbase = reinterpret_cast<const T*>(ring + (size_t)stage * kLinStageBytes);
+        if (p.mma) {
+            // Tensor-core path: the chunk's rows (at most sixteen) are the rows of one m16n8k16 tile, the tokens its
+            // eight columns.  Warp w contracts the w-th eighth of the inner dimension for the whole tile: per 32-wide
+            // slice one 128-bit load per operand (rows g and g + 8 of the weights, token g of x; same permutation of
+            // the contraction index on both, see mk36_mma.cuh) and two MMAs.  The eight partial tiles meet in shared
+            // memory (two buffers, so one block-wide barrier per chunk), 128 threads finish one output each.
+            const int g = lane >> 2, t = lane & 3;
+            const int nsl = p.K >> 8;  // 32-wide slices per warp
+            float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+            const T* alo = sbase + (size_t)g * rowK + 8 * t;
+            const T* ahi = sbase + (size_t)(g + 8) * rowK + 8 * t;
+            const T* bx = xs + (size_t)g * rowK + 8 * t;
+            const bool lo_live = g < count, hi_live = g + 8 < count;
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll 4
+            for (int sl = 0; sl < nsl; ++sl) {
+                const int kb = (warp * nsl + sl) * 32;
+                const uint4 a0 = lo_live ? lds128(alo + kb) : zero;
+                const uint4 a1 = hi_live ? lds128(ahi + kb) : zero;
+                const uint4 bb = lds128(bx + kb);
+                mma_slice32<T>(d0, d1, a0, a1, bb);
+            }
+            float* red = reinterpret_cast<float*>(smem + p.off_red) + (size_t)(k & 1) * (kLinConsumerWarps * kLinMmaRows * 8);
+            float* mine = red + (size_t)warp * (kLinMmaRows * 8);
+            *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(d0[0] + d1[0], d0[1] + d1[1]);
+            *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(d0[2] + d1[2], d0[3] + d1[3]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // the weights of this stage have been read
+            if (++stage == R) { stage = 0; ++use; }
+            named_barrier(1, kLinConsumerThreads);
+            if (tid < kLinMmaRows * 8) {
+                const int row = tid >> 3, tok = tid & 7;
+                if (row < count && tok < p.ntok) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kLinConsumerWarps; ++w) v += red[(size_t)w * (kLinMmaRows * 8) + tid];
+                    const int n = first + row;
+                    const size_t o = (size_t)tok * p.N + n;
+                    if (resid) v += to_float<T>(resid[o]);
+                    const T rounded = from_float<T>(v);
+                    out[o] = rounded;
+                    if (p.argmax) {
+                        const unsigned long long key = argmax_key(to_float<T>(rounded), n);
+                        best0 = key > best0 ? key : best0;  // this thread's token is tid % 8 in every chunk
+                    }
+                }
+            }
+            continue;
+        }
         if (p.ntok > 2) {
             // groups of four rows, four tokens per pass: group g of the chunk goes to warp (slot + g) % warps
             const int groups = (count + 3) >> 2;
@@ -456,7 +519,9 @@ __global__ void __launch_bounds__(kLinThreads, 1) linear_decode_kernel(const Lin
     if (tid == 0 && cta == ncta - 1) trace_stamp(p.ctl, 3);
 
     // ---- arg-max: CTA-wide maxima first ----
-    if (p.argmax && lane < 16) {
+    if (p.argmax && p.mma) {
+        if (tid < kLinMmaRows * 8 && best0 != 0ull) atomicMax(&s_best[tid & 7], best0);
+    } else if (p.argmax && lane < 16) {
         if (best0 != 0ull) atomicMax(&s_best[lane & 3], best0);
         if (best1 != 0ull) atomicMax(&s_best[4 + (lane & 3)], best1);
     }
@@ -502,8 +567,9 @@ int mk36_linear_decode(const mk36_linear_args* a, void* workspace, size_t worksp
     if (a->batch > kLinMaxTokens) MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: at most %d tokens per call (got %d)", kLinMaxTokens, a->batch);
     if (K % 8 != 0 || (size_t)K * 2 > (size_t)kLinStageBytes || K > 8 * kLinMaxPieces * kLinConsumerThreads)
         MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: in_features must be a multiple of 8 and at most %d (got %d)", kLinStageBytes / 2, K);
-    if ((size_t)(a->batch > 2 ? (a->batch + 3) / 4 * 4 : a->batch) * K * 2 > 65536)
-        MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: batch x in_features x 2 bytes must fit 64 KB of shared memory");
+    const bool p_mma_hint = options().linear_mma > 0 && a->batch >= options().linear_mma && K % 256 == 0;
+    if ((size_t)((a->batch > 2 || p_mma_hint) ? kLinMaxTokens : a->batch) * K * 2 > 98304)
+        MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: the tokens (eight columns when there are more than two) x in_features x 2 bytes must fit 96 KB of shared memory");
     if ((long long)N * K >= (1ll << 40) || N >= (1 << 30)) MK36_FAIL(MK36_ERR_UNSUPPORTED, "linear_decode: out_features too large");
     const void* ptrs[] = {a->x, a->weight, a->norm_weight, a->residual, a->out};
     for (const void* q : ptrs)
@@ -527,7 +593,10 @@ int mk36_linear_decode(const mk36_linear_args* a, void* workspace, size_t worksp
     p.K = K;
     p.N = N;
     p.eps = a->eps;
+    // three to eight tokens: tensor-core tiles when the inner dimension splits into 32-wide slices over the eight warps
+    p.mma = (options().linear_mma > 0 && a->batch >= options().linear_mma && K % 256 == 0) ? 1 : 0;
     p.rows = kLinStageBytes / (K * 2);
+    if (p.mma && p.rows > kLinMmaRows) p.rows = kLinMmaRows;
     p.nchunks = (N + p.rows - 1) / p.rows;
     {
         const int ppt = (K / 8 + kLinConsumerThreads - 1) / kLinConsumerThreads;
@@ -542,7 +611,8 @@ int mk36_linear_decode(const mk36_linear_args* a, void* workspace, size_t worksp
         return (int)at;
     };
     p.off_bars = take(2 * kLinMaxStages * 8, 16);
-    const int xtok = a->batch > 2 ? (a->batch + 3) / 4 * 4 : a->batch;  // groups of three tokens read a fourth vector
+    const int xtok = p.mma ? kLinMaxTokens : (a->batch > 2 ? (a->batch + 3) / 4 * 4 : a->batch);  // groups of three tokens read a fourth vector
+    p.off_red = take(p.mma ? (size_t)2 * kLinConsumerWarps * kLinMmaRows * 8 * 4 : 0, 16);
     p.off_x = take((size_t)xtok * K * 2, 128);
     p.off_ring = take(0, 128);
     const long long room = (long long)dev->max_smem_optin - (long long)off - 1024;

@@ -183,6 +183,10 @@ int mk36_set_option(const char* name, int value) {
         options().moe_dyn_rounds = value > 0 ? value : 0;
         return MK36_OK;
     }
+    if (std::strcmp(name, "linear_mma") == 0) {
+        options().linear_mma = value < 0 ? 0 : value;
+        return MK36_OK;
+    }
     if (std::strcmp(name, "moe_static") == 0) {
         options().moe_static = value ? 1 : 0;
         return MK36_OK;

@@ -84,6 +84,7 @@ struct Options {
     int attn_stream = 1;    // 0: attention calls skip the streaming kernel (shared-memory ring) and use the register-staged one
     int dense_stream = 1;   // 0: one-token dense FFN calls use the tensor-core kernel instead of the streaming kernel
     int moe_dyn_rounds = 0; // > 0: rounds of gate/up chunks at the end of the stream dealt through the work counter (default: 4 in the stream kernel, 2 in the batch kernel)
+    int linear_mma = 3;     // fewest tokens for which a projection runs on tensor-core tiles (0: never)
     int moe_static = 0;     // 1: the MoE stream kernel deals its gate/up chunks statically (no work counter)
     int static_scratch_limit = 0;  // > 0: mk36_full_attention_decode_static treats its array as this many bytes (test hook)
 };

@@ -658,6 +658,36 @@ def test_linear_decode_matches_oracle(batch, k, n, dtype, norm, residual, cuda_d
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("batch,k,n", [(3, 256, 77), (5, 1024, 4099), (8, 2048, 5120)])
+def test_linear_decode_plain_fma_path_for_several_tokens(batch, k, n, cuda_device):
+    """Three to eight tokens normally run on tensor-core tiles; the plain-FMA path (four rows x four tokens per
+    warp), which also serves inner dimensions that are not a multiple of 256, must give the same answer."""
+    import mega_kernel_qwen36 as mk
+    from mega_kernel_qwen36 import cabi, synthetic as syn
+    from oracle import decode_oracle as oracle
+
+    t = syn.projection_tensors(k, n, batch, seed=77, norm=True, residual=True)
+    d = {name: v.to(cuda_device) for name, v in t.items()}
+    lib = cabi.load()
+    tiles, best_tiles = mk.linear_decode(d["x"], d["weight"], norm_weight=d["norm_weight"], residual=d["residual"], return_argmax=True)
+    cabi.check(lib.mk36_set_option(b"linear_mma", 0))
+    try:
+        plain, best_plain = mk.linear_decode(d["x"], d["weight"], norm_weight=d["norm_weight"], residual=d["residual"], return_argmax=True)
+    finally:
+        cabi.check(lib.mk36_set_option(b"linear_mma", 3))
+    ref = oracle.linear_decode(t["x"], t["weight"], norm_weight=t["norm_weight"], residual=t["residual"])
+    assert_output_parity(plain.cpu(), ref, what="plain-FMA path")
+    assert_output_parity(tiles.cpu(), ref, what="tensor-core path")
+    for out, best in ((tiles, best_tiles), (plain, best_plain)):
+        row_max = out.float().max(dim=-1, keepdim=True).values
+        assert torch.equal(best, (out.float() == row_max).float().argmax(dim=-1))
+    # inner dimension not a multiple of 256: served by the plain path whatever the switch says
+    t2 = syn.projection_tensors(k + 8, n, batch, seed=78, norm=True, residual=False)
+    d2 = {name: v.to(cuda_device) for name, v in t2.items()}
+    got = mk.linear_decode(d2["x"], d2["weight"], norm_weight=d2["norm_weight"]).cpu()
+    assert_output_parity(got, oracle.linear_decode(t2["x"], t2["weight"], norm_weight=t2["norm_weight"]), what="odd inner dimension")
+
+
 @pytest.mark.parametrize("batch,n", [(1, 30_001), (4, 248_320), (7, 9_000)])
 def test_linear_decode_argmax_is_the_argmax_of_the_stored_row(batch, n, cuda_device):
     """LM-head use: the arg-max comes from the same launch; lowest index among equal (rounded) values."""
