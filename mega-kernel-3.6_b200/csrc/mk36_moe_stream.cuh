@@ -43,7 +43,8 @@ struct MoeStreamParams {
     float* route_w;
     float* partial_out;
     Control* ctl;
-    unsigned long long* mailbox;  // [ctas][kTagSlots] tagged logits, one copy per receiving CTA
+    unsigned long long* mailbox;  // [boxes][box_stride] tagged logits, one copy per receiving CTA (or group of CTAs)
+    int box_stride;               // words per mailbox: tokens x experts rounded up to 512 (at most kTagSlots)
     float* act;   // [ntok*K][I]   silu(gate) * up of the routed pairs
     float* sact;  // [ntok][Is]    same for the shared expert
     int ntok, H, E, K, I, Is;

@@ -577,7 +577,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
             const int v = it / nbox, dest = it - v * nbox;
             const int row = v % nrows, b = v / nrows;
             const unsigned long long word = tagbits | (unsigned long long)__float_as_uint(s_pub[v]);
-            st_relaxed_u64(p.mailbox + (size_t)dest * kTagSlots + b * p.E + r0 + row, word);
+            st_relaxed_u64(p.mailbox + (size_t)dest * p.box_stride + b * p.E + r0 + row, word);
         }
     }
     if (tracer) trace_stamp(p.ctl, 2);
@@ -586,7 +586,7 @@ __global__ void __launch_bounds__(kStThreads, 1) moe_decode_batch_kernel(const M
     // ---- routing: warp b takes token b ----
     if (warp < p.ntok && *(volatile int*)&s_abort == 0) {
         RouteArgs ra;
-        ra.box = p.mailbox + (size_t)(cta / p.box_share) * kTagSlots;
+        ra.box = p.mailbox + (size_t)(cta / p.box_share) * p.box_stride;
         ra.ctl = p.ctl;
         ra.indices = (cta == 0) ? p.indices : nullptr;
         ra.route_w = (cta == 0) ? p.route_w : nullptr;
@@ -915,6 +915,7 @@ int moe_decode_batch_launch(const mk36_moe_args* a, const mk36_comm* comm, void*
     for (int b0 = 0; b0 < a->batch; b0 += tb) {
         p.ntok = (a->batch - b0 < tb) ? (a->batch - b0) : tb;
         p.box_share = p.ntok;
+        p.box_stride = (p.ntok * E + 511) / 512 * 512;
         p.x = static_cast<const unsigned char*>(a->x) + (size_t)b0 * H * es;
         p.out = a->out ? static_cast<unsigned char*>(a->out) + (size_t)b0 * H * es : nullptr;
         p.partial_out = a->partial_out ? a->partial_out + (size_t)b0 * H : nullptr;
