@@ -410,6 +410,10 @@ typedef struct mk36_comm {
 
 MK36_API size_t mk36_comm_buffer_bytes(void);
 MK36_API int mk36_comm_buffer_alloc(void** buffer);
+/* Clears the rank's OWN buffer (step counter, slots) on `stream`: the way back after a step in which a rank gave up
+ * on a peer (status 401), which leaves the ranks' step counters in disagreement.  Every rank calls it, with a host
+ * barrier before and after; workspaces whose status was set need mk36_workspace_init as well. */
+MK36_API int mk36_comm_buffer_reset(void* buffer, void* stream);
 MK36_API int mk36_comm_buffer_free(void* buffer);
 MK36_API int mk36_ipc_export(void* buffer, unsigned char handle[MK36_IPC_HANDLE_BYTES]);
 MK36_API int mk36_ipc_open(const unsigned char handle[MK36_IPC_HANDLE_BYTES], void** buffer);

@@ -50,6 +50,17 @@ int mk36_comm_buffer_alloc(void** buffer) {
     return MK36_OK;
 }
 
+// Puts the rank's own buffer back into the state mk36_comm_buffer_alloc left it in (step counter and every slot
+// zero), on `stream`.  After a step in which a rank gave up on a peer the ranks' step counters disagree for good;
+// this is the way back without a new allocation and a new IPC exchange.  Collective in spirit: every rank resets
+// its own buffer, with a host barrier before (no rank is still inside a step) and after (nobody starts the next
+// step against a buffer that is not clear yet); the workspaces whose status was set need mk36_workspace_init too.
+int mk36_comm_buffer_reset(void* buffer, void* stream) {
+    if (!buffer) MK36_FAIL(MK36_ERR_INVALID_ARG, "comm_buffer_reset: buffer is NULL");
+    MK36_CUDA_OK(cudaMemsetAsync(buffer, 0, kCommBytes, static_cast<cudaStream_t>(stream)));
+    return MK36_OK;
+}
+
 int mk36_comm_buffer_free(void* buffer) {
     if (buffer) MK36_CUDA_OK(cudaFree(buffer));
     return MK36_OK;

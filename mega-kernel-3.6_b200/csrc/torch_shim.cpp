@@ -232,6 +232,10 @@ int64_t comm_buffer_alloc() {
     return static_cast<int64_t>(reinterpret_cast<uintptr_t>(p));
 }
 
+void comm_buffer_reset(int64_t ptr) {
+    check_rc(mk36_comm_buffer_reset(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)), at::cuda::getCurrentCUDAStream().stream()));
+}
+
 void comm_buffer_free(int64_t ptr) { check_rc(mk36_comm_buffer_free(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)))); }
 
 py::bytes ipc_export(int64_t ptr) {
@@ -558,6 +562,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("moe_decode_ep", &moe_decode_ep, "expert-parallel MoE decode with the cross-GPU sum fused into the kernel");
     m.def("dense_ffn_decode_tp", &dense_ffn_decode_tp, "tensor-parallel dense FFN decode with the cross-GPU sum fused into the kernel");
     m.def("comm_buffer_alloc", &comm_buffer_alloc, "allocate and clear this rank's exchange buffer; returns its device pointer");
+    m.def("comm_buffer_reset", &comm_buffer_reset, "clear this rank's exchange buffer on the current stream");
     m.def("comm_buffer_free", &comm_buffer_free);
     m.def("ipc_export", &ipc_export, "CUDA IPC handle of an exchange buffer");
     m.def("ipc_open", &ipc_open, "map a peer's exchange buffer; returns the device pointer in this process");

@@ -113,6 +113,7 @@ SIGNATURES = {
     "mk36_linear_attention_decode_steps": (C.c_int, [C.POINTER(LinearAttentionStepsArgs), C.c_void_p]),
     "mk36_comm_buffer_bytes": (C.c_size_t, []),
     "mk36_comm_buffer_alloc": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "mk36_comm_buffer_reset": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mk36_comm_buffer_free": (C.c_int, [C.c_void_p]),
     "mk36_ipc_export": (C.c_int, [C.c_void_p, C.POINTER(C.c_ubyte)]),
     "mk36_ipc_open": (C.c_int, [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)]),

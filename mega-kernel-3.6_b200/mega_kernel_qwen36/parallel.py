@@ -126,6 +126,17 @@ class PeerExchange:
         self.buffers = [self._own if q == self.rank else self._peers[q] for q in range(self.world)]
         dist.barrier(group=group)  # every buffer is cleared and mapped everywhere before the first step
 
+    def reset(self, group: Optional[dist.ProcessGroup] = None) -> None:
+        """Collective: clears every rank's buffer (step counters and slots).  The way back after a step in which a
+        rank gave up waiting for a peer, which leaves the ranks' step counters in disagreement; the workspaces
+        whose status was set must be re-initialised as well (``workspace_reset`` of the extension)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            dist.barrier(group=group)  # no rank is still inside a step
+            self._ext.comm_buffer_reset(self._own)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)  # nobody starts the next step against a buffer that is not clear yet
+
     def close(self) -> None:
         """Unmaps the peers' buffers and frees the own one.  Collective in spirit: no rank may still
         be inside a step that uses this object."""

@@ -336,3 +336,11 @@ def test_extension_errors_with_formatted_numbers_raise_instead_of_crashing():
     ) % str(Path(mk.__file__).resolve().parent.parent)
     proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0 and "raised" in proc.stdout, (proc.returncode, proc.stderr[-500:])
+
+
+def test_exchange_buffer_reset_checks_its_argument():
+    from mega_kernel_qwen36 import cabi
+
+    lib = cabi.load()
+    assert lib.mk36_comm_buffer_reset(None, None) == cabi.MK36_ERR_INVALID_ARG
+    assert b"buffer is NULL" in lib.mk36_last_error()
