@@ -119,6 +119,18 @@ def main() -> int:
                     failures.append(f"{name} step {step}: device status {status}")
                 check(parity.assert_output_parity, out.cpu(), ro, f"{name} fused step {step}")
                 same_on_all_ranks(out, f"{name} step {step}")
+            if name == "dense_mid_bf16":
+                # the way back after a failed step: clear every rank's exchange buffer (the counters stand at an odd
+                # step here), then the same call must give the same bits again
+                before = out.clone()
+                exchange.reset()
+                for step in range(2):
+                    again = parallel.dense_ffn_decode_tp(x.to(device), local, exchange=exchange)
+                    torch.cuda.synchronize()
+                    if not torch.equal(again, before):
+                        failures.append(f"{name}: step {step} after the exchange reset differs")
+                if mk.ops._C.workspace_status(again) != 0:
+                    failures.append(f"{name}: device status set after the exchange reset")
             del local, host, full, cut
             torch.cuda.empty_cache()
         # ---------------- attention, KV-head parallel (no exchange; only where the head count allows) ----------------
